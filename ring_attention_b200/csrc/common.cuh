@@ -1,0 +1,110 @@
+// Shared host/device helpers of the library: status handling, the device status word
+// that bounded waits report into, and the position maps every step kernel uses.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/ring_attention_b200.h"
+
+// The cache handle of the C ABI: K and V of shape (batch, kv_heads, s_max, head_dim).
+struct ra_kv_cache {
+  int dtype, batch, kv_heads, s_max, head_dim, current_len;
+  void* k;
+  void* v;
+};
+
+namespace rab {
+
+// ---- host-side error reporting -------------------------------------------------
+void set_error(const char* fmt, ...);
+const char* last_error();
+
+#define RAB_CUDA(expr)                                                                  \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess) {                                                            \
+      ::rab::set_error("CUDA error '%s' at %s:%d in %s", cudaGetErrorString(_e), __FILE__, \
+                       __LINE__, #expr);                                                \
+      return RA_ERR_CUDA;                                                               \
+    }                                                                                   \
+  } while (0)
+
+#define RAB_REQUIRE(cond, code, ...)  \
+  do {                                \
+    if (!(cond)) {                    \
+      ::rab::set_error(__VA_ARGS__);  \
+      return (code);                  \
+    }                                 \
+  } while (0)
+
+inline int kv_heads_of(const ra_shape& s) { return s.kv_heads > 0 ? s.kv_heads : s.heads; }
+
+// ---- device status word ----------------------------------------------------------
+// One per device (a __device__ array in status.cu). A kernel whose bounded wait runs out
+// records {code, which wait, block, tile} and every later block of any kernel in this
+// library returns at once, so a protocol bug costs seconds, never a hung GPU.
+int* device_status_ptr();  // device address of the 4-int status word of the current device
+int read_device_status(int out[4], bool clear);
+
+// ---- position maps ------------------------------------------------------------------
+// Kernel-side copy of a segment map: local row i -> base[i / seg_len] + (i % seg_len) * stride.
+struct PosMap {
+  int n_seg;
+  int seg_len;
+  int base[RA_MAX_SEG];
+};
+
+inline PosMap make_posmap(const ra_segmap& s) {
+  PosMap p;
+  p.n_seg = s.n_seg;
+  p.seg_len = s.seg_len;
+  for (int i = 0; i < RA_MAX_SEG; ++i) p.base[i] = i < s.n_seg ? s.base[i] : 0;
+  return p;
+}
+
+inline PosMap affine_posmap(int offset, int len) {
+  PosMap p;
+  std::memset(&p, 0, sizeof(p));
+  p.n_seg = 1;
+  p.seg_len = len > 0 ? len : 1;
+  p.base[0] = offset;
+  return p;
+}
+
+// Arguments shared by the SIMT and the tcgen05 step kernels.
+struct StepArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  float* out;
+  float* m;
+  float* l;
+  int B, H, kvH, Sq, Sk, D;
+  long long kv_head_stride;  // elements between consecutive KV heads (rows * D)
+  PosMap qmap, kmap;
+  int stride;
+  unsigned flags;
+  long long doc_len;
+  int* status;
+};
+
+int launch_step_simt(int dtype, const StepArgs& a, cudaStream_t stream);
+int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream);
+bool step_tc_supported(int dtype, const StepArgs& a);
+
+// seq_q == 1 split-K decode step (decode.cu); workspace NULL = per-device buffer.
+int decode_step(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
+                float* l, const ra_shape& s, int q_offset, int k_offset, int causal,
+                cudaStream_t stream, int kv_row_stride, void* ws, size_t ws_bytes);
+
+int launch_init(float* out, float* m, float* l, size_t out_count, size_t m_count,
+                cudaStream_t stream);
+int launch_finalize(float* out, const float* l, size_t rows, int D, cudaStream_t stream);
+
+}  // namespace rab

@@ -1,0 +1,530 @@
+// Split-K decode (seq_q == 1) against a KV cache read in place: the HBM-bound half of the
+// hot path. Replaces the reference's split + reduce kernels (src/attention_decode.cu:73-277).
+//
+// What bounds it: every K and V row of the local shard is read exactly once from HBM, so
+// the kernel is built around bytes in flight, not arithmetic.
+//  - One block per (split, KV head, batch row) serves ALL query heads that map to that KV
+//    head (h % kv_heads), so grouped-query attention reads each cached row once instead of
+//    once per query head (the reference re-reads it per head, src/attention_decode.cu:88).
+//  - K/V rows stream through a 4-stage shared-memory ring filled with 16-byte cp.async
+//    copies (fully coalesced: consecutive threads copy consecutive 16-byte pieces of
+//    consecutive rows), which keeps tens of KB per SM in flight without holding them in
+//    registers.
+//  - A group of `LPR` lanes owns a row: each lane keeps its slice of q (pre-scaled) for every
+//    head of the group, the dot product finishes with log2(LPR) shuffles, and each lane
+//    group carries its own running (m, l, out) so no cross-lane traffic is needed until
+//    the end, where a warp-shuffle log-sum-exp merge and one shared-memory pass combine the
+//    lane groups and warps of the block.
+//  - The split count is chosen so the grid is about three waves of the SM count.
+// Partials (m, l, out) per (split, batch, head) go to a workspace; a second tiny kernel
+// folds them into the persistent state (src/attention_decode.cu:228-277 does the same for
+// its fixed 8 splits).
+#include <algorithm>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace rab {
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 4;
+constexpr int kMaxSplits = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+__device__ inline float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ inline void cp_async16(void* smem_dst, const void* gsrc, int src_bytes) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc),
+               "r"(src_bytes)
+               : "memory");
+}
+__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ inline void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Unpack one 16-byte piece into floats.
+template <typename T>
+struct Piece;
+template <>
+struct Piece<float> {
+  static constexpr int kElems = 4;
+  __device__ static void unpack(const uint4& u, float* f) {
+    f[0] = __uint_as_float(u.x);
+    f[1] = __uint_as_float(u.y);
+    f[2] = __uint_as_float(u.z);
+    f[3] = __uint_as_float(u.w);
+  }
+};
+template <>
+struct Piece<__half> {
+  static constexpr int kElems = 8;
+  __device__ static void unpack(const uint4& u, float* f) {
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = x.x;
+      f[2 * i + 1] = x.y;
+    }
+  }
+};
+template <>
+struct Piece<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  __device__ static void unpack(const uint4& u, float* f) {
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // bf16 -> fp32 is a 16-bit shift
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+template <typename T, int D>
+struct DecodeCfg {
+  static constexpr int kRowBytes = D * static_cast<int>(sizeof(T));
+  static constexpr int kPieces = kRowBytes / 16;  // 16-byte pieces per row
+  // lanes per row: every lane owns 1..4 pieces
+  static constexpr int kLPR = kPieces >= 32 ? 16 : (kPieces >= 8 ? 8 : 4);
+  static constexpr int kVPT = kPieces / kLPR;               // pieces per lane
+  static constexpr int kEPL = kVPT * Piece<T>::kElems;      // elements per lane
+  static constexpr int kRowsPerWarpStep = 32 / kLPR;
+  static constexpr int kRowsPerStep = kWarps * kRowsPerWarpStep;
+  static constexpr int kSteps =
+      (8192 / (kRowsPerStep * kRowBytes)) > 0 ? (8192 / (kRowsPerStep * kRowBytes)) : 1;
+  static constexpr int kRowsPerStage = kRowsPerStep * kSteps;
+  static constexpr int kStageBytes = kRowsPerStage * kRowBytes;  // per tensor
+  static constexpr int kSmemBytes = 2 * kStages * kStageBytes;
+};
+
+// grid = (n_split, kv_heads * head_batches, batch). GB = query heads handled per block.
+template <typename T, int D, int GB>
+__global__ void __launch_bounds__(kThreads)
+    decode_split_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
+                        float* __restrict__ Mp, float* __restrict__ Lp, float* __restrict__ Op,
+                        int B, int H, int kvH, int sk_eff, long long kv_head_stride,
+                        int rows_per_split, int head_batches, float scale_log2) {
+  using C = DecodeCfg<T, D>;
+  extern __shared__ __align__(16) unsigned char smem[];
+  unsigned char* k_ring = smem;
+  unsigned char* v_ring = smem + kStages * C::kStageBytes;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int lr = lane % C::kLPR;       // lane within the row group
+  const int grp = lane / C::kLPR;      // row group within the warp
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / head_batches;
+  const int hb = blockIdx.y % head_batches;
+  const int b = blockIdx.z;
+
+  // Query heads of this block: h = kvh + kvH * (hb * GB + g), while h < H.
+  float q_reg[GB][C::kEPL];
+  float o_reg[GB][C::kEPL];
+  float m_run[GB], l_run[GB];
+#pragma unroll
+  for (int g = 0; g < GB; ++g) {
+    const int h = kvh + kvH * (hb * GB + g);
+    m_run[g] = -INFINITY;
+    l_run[g] = 0.f;
+#pragma unroll
+    for (int v = 0; v < C::kVPT; ++v) {
+      float f[Piece<T>::kElems];
+      if (h < H) {
+        const uint4 u = *reinterpret_cast<const uint4*>(
+            reinterpret_cast<const unsigned char*>(Q + (static_cast<size_t>(b) * H + h) * D) +
+            (v * C::kLPR + lr) * 16);
+        Piece<T>::unpack(u, f);
+      } else {
+#pragma unroll
+        for (int e = 0; e < Piece<T>::kElems; ++e) f[e] = 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < Piece<T>::kElems; ++e) {
+        q_reg[g][v * Piece<T>::kElems + e] = f[e] * scale_log2;
+        o_reg[g][v * Piece<T>::kElems + e] = 0.f;
+      }
+    }
+  }
+
+  const int row_begin = split * rows_per_split;
+  const int row_end = min(sk_eff, row_begin + rows_per_split);
+  const int n_rows = max(0, row_end - row_begin);
+  const int n_stages = (n_rows + C::kRowsPerStage - 1) / C::kRowsPerStage;
+  const unsigned char* k_base = reinterpret_cast<const unsigned char*>(
+      K + (static_cast<size_t>(b) * kvH + kvh) * kv_head_stride);
+  const unsigned char* v_base = reinterpret_cast<const unsigned char*>(
+      V + (static_cast<size_t>(b) * kvH + kvh) * kv_head_stride);
+
+  auto issue = [&](int st) {
+    if (st < n_stages) {
+      const int slot = st % kStages;
+      const long long first = static_cast<long long>(row_begin) + st * C::kRowsPerStage;
+      const long long valid_bytes =
+          (static_cast<long long>(row_end) - first) * C::kRowBytes;  // > 0
+      const size_t goff = static_cast<size_t>(first) * C::kRowBytes;
+      for (int p = tid; p < C::kStageBytes / 16; p += kThreads) {
+        const long long off = static_cast<long long>(p) * 16;
+        const bool ok = off < valid_bytes;
+        // past the split: src-size 0 zero-fills the destination, the source is not read
+        cp_async16(k_ring + slot * C::kStageBytes + off, ok ? k_base + goff + off : k_base,
+                   ok ? 16 : 0);
+        cp_async16(v_ring + slot * C::kStageBytes + off, ok ? v_base + goff + off : v_base,
+                   ok ? 16 : 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) issue(s);
+
+  for (int st = 0; st < n_stages; ++st) {
+    cp_async_wait<kStages - 2>();
+    __syncthreads();
+    issue(st + kStages - 1);
+    const int slot = st % kStages;
+    const int stage_row0 = st * C::kRowsPerStage;
+#pragma unroll 1
+    for (int step = 0; step < C::kSteps; ++step) {
+      const int rl = step * C::kRowsPerStep + warp * C::kRowsPerWarpStep + grp;
+      const bool valid = stage_row0 + rl < n_rows;
+      const unsigned char* krow = k_ring + slot * C::kStageBytes + rl * C::kRowBytes;
+      const unsigned char* vrow = v_ring + slot * C::kStageBytes + rl * C::kRowBytes;
+      float kf[C::kEPL];
+#pragma unroll
+      for (int v = 0; v < C::kVPT; ++v) {
+        const uint4 u = *reinterpret_cast<const uint4*>(krow + (v * C::kLPR + lr) * 16);
+        Piece<T>::unpack(u, &kf[v * Piece<T>::kElems]);
+      }
+      float s[GB];
+#pragma unroll
+      for (int g = 0; g < GB; ++g) {
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < C::kEPL; ++e) acc = fmaf(q_reg[g][e], kf[e], acc);
+        s[g] = acc;
+      }
+#pragma unroll
+      for (int off = 1; off < C::kLPR; off <<= 1) {
+#pragma unroll
+        for (int g = 0; g < GB; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
+      }
+      float vf[C::kEPL];
+#pragma unroll
+      for (int v = 0; v < C::kVPT; ++v) {
+        const uint4 u = *reinterpret_cast<const uint4*>(vrow + (v * C::kLPR + lr) * 16);
+        Piece<T>::unpack(u, &vf[v * Piece<T>::kElems]);
+      }
+      if (valid) {
+#pragma unroll
+        for (int g = 0; g < GB; ++g) {
+          if (s[g] > m_run[g]) {  // rare after the first rows: rescale only when the max moves
+            const float alpha = ex2(m_run[g] - s[g]);  // ex2(-inf) = 0 on the first row
+            l_run[g] *= alpha;
+#pragma unroll
+            for (int e = 0; e < C::kEPL; ++e) o_reg[g][e] *= alpha;
+            m_run[g] = s[g];
+          }
+          const float p = ex2(s[g] - m_run[g]);
+          l_run[g] += p;
+#pragma unroll
+          for (int e = 0; e < C::kEPL; ++e) o_reg[g][e] = fmaf(p, vf[e], o_reg[g][e]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // Merge the row groups of the warp (log-sum-exp merge through shuffles) ...
+#pragma unroll
+  for (int off = C::kLPR; off < 32; off <<= 1) {
+#pragma unroll
+    for (int g = 0; g < GB; ++g) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m_run[g], off);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l_run[g], off);
+      const float m_n = fmaxf(m_run[g], m_o);
+      const float a = (m_run[g] == -INFINITY) ? 0.f : ex2(m_run[g] - m_n);
+      const float c = (m_o == -INFINITY) ? 0.f : ex2(m_o - m_n);
+      l_run[g] = a * l_run[g] + c * l_o;
+#pragma unroll
+      for (int e = 0; e < C::kEPL; ++e) {
+        const float o_o = __shfl_xor_sync(0xffffffffu, o_reg[g][e], off);
+        o_reg[g][e] = a * o_reg[g][e] + c * o_o;
+      }
+      m_run[g] = m_n;
+    }
+  }
+  // ... then the warps of the block through shared memory (the ring is idle now).
+  __syncthreads();
+  float* red_m = reinterpret_cast<float*>(smem);            // [kWarps][GB]
+  float* red_l = red_m + kWarps * GB;                        // [kWarps][GB]
+  float* red_o = red_l + kWarps * GB;                        // [kWarps][GB][D]
+  if (grp == 0) {
+#pragma unroll
+    for (int g = 0; g < GB; ++g) {
+      if (lr == 0) {
+        red_m[warp * GB + g] = m_run[g];
+        red_l[warp * GB + g] = l_run[g];
+      }
+#pragma unroll
+      for (int v = 0; v < C::kVPT; ++v)
+#pragma unroll
+        for (int e = 0; e < Piece<T>::kElems; ++e)
+          red_o[(warp * GB + g) * D + (v * C::kLPR + lr) * Piece<T>::kElems + e] =
+              o_reg[g][v * Piece<T>::kElems + e];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < GB * D; idx += kThreads) {
+    const int g = idx / D;
+    const int d = idx - g * D;
+    const int h = kvh + kvH * (hb * GB + g);
+    if (h >= H) continue;
+    float m_n = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) m_n = fmaxf(m_n, red_m[w * GB + g]);
+    float o_acc = 0.f, l_acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float mw = red_m[w * GB + g];
+      const float sc = (mw == -INFINITY) ? 0.f : ex2(mw - m_n);
+      o_acc += sc * red_o[(w * GB + g) * D + d];
+      l_acc += sc * red_l[w * GB + g];
+    }
+    const size_t prow = (static_cast<size_t>(split) * B + b) * H + h;
+    Op[prow * D + d] = o_acc;
+    if (d == 0) {
+      Mp[prow] = m_n * kLn2;  // back to natural-log units, the unit of the persistent state
+      Lp[prow] = l_acc;
+    }
+  }
+}
+
+// Fold n_split partials into the persistent (out, m, l). grid = (H, B), block = D threads.
+__global__ void decode_reduce_kernel(const float* __restrict__ Mp, const float* __restrict__ Lp,
+                                     const float* __restrict__ Op, float* __restrict__ M,
+                                     float* __restrict__ L, float* __restrict__ O, int B, int H,
+                                     int D, int n_split) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const size_t row = static_cast<size_t>(b) * H + h;
+  const float m_old = M[row];
+  float m_n = m_old;
+  for (int s = 0; s < n_split; ++s) m_n = fmaxf(m_n, Mp[(static_cast<size_t>(s) * B + b) * H + h]);
+  if (m_n == -INFINITY) return;  // nothing visible anywhere: the state stays as it is
+  const float a = (m_old == -INFINITY) ? 0.f : expf(m_old - m_n);
+  float o_acc = a * O[row * D + d];
+  float l_acc = a * L[row];
+  for (int s = 0; s < n_split; ++s) {
+    const size_t prow = (static_cast<size_t>(s) * B + b) * H + h;
+    const float ms = Mp[prow];
+    const float sc = (ms == -INFINITY) ? 0.f : expf(ms - m_n);
+    o_acc += sc * Op[prow * D + d];
+    l_acc += sc * Lp[prow];
+  }
+  O[row * D + d] = o_acc;
+  __syncthreads();  // every thread has read M/L before thread 0 overwrites them
+  if (d == 0) {
+    M[row] = m_n;
+    L[row] = l_acc;
+  }
+}
+
+struct Plan {
+  int n_split;
+  int rows_per_split;
+  int gb;
+  int head_batches;
+};
+
+int sm_count() {
+  int dev = 0, v = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+  return v > 0 ? v : 148;
+}
+
+Plan make_plan(int B, int H, int kvH, int sk_eff, int rows_per_stage, int sms) {
+  Plan p;
+  const int group = (H + kvH - 1) / kvH;  // query heads per KV head (largest group)
+  p.gb = group > 4 ? 8 : (group > 2 ? 4 : (group > 1 ? 2 : 1));  // smallest of 1/2/4/8 that fits
+  p.head_batches = (group + p.gb - 1) / p.gb;
+  const int blocks_per_split = B * kvH * p.head_batches;
+  int want = (3 * sms + blocks_per_split - 1) / blocks_per_split;
+  const int max_by_rows = std::max(1, sk_eff / (2 * rows_per_stage));
+  want = std::max(1, std::min(std::min(want, max_by_rows), kMaxSplits));
+  int rps = (sk_eff + want - 1) / want;
+  rps = ((rps + rows_per_stage - 1) / rows_per_stage) * rows_per_stage;
+  if (rps < rows_per_stage) rps = rows_per_stage;
+  p.rows_per_split = rps;
+  p.n_split = std::max(1, (sk_eff + rps - 1) / rps);
+  return p;
+}
+
+// Per-device workspace that grows on demand, like the reference's process-static buffer
+// (src/attention_decode.cu:55-65). Not safe for concurrent streams, as the reference's.
+struct DevWorkspace {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+DevWorkspace g_ws[64];
+std::mutex g_ws_mu;
+
+int ensure_workspace(size_t need, void** out) {
+  int dev = 0;
+  RAB_CUDA(cudaGetDevice(&dev));
+  RAB_REQUIRE(dev >= 0 && dev < 64, RA_ERR_INVALID, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_ws_mu);
+  DevWorkspace& w = g_ws[dev];
+  if (w.bytes < need) {
+    if (w.ptr) RAB_CUDA(cudaFree(w.ptr));
+    w.ptr = nullptr;
+    w.bytes = 0;
+    RAB_CUDA(cudaMalloc(&w.ptr, need));
+    w.bytes = need;
+  }
+  *out = w.ptr;
+  return RA_OK;
+}
+
+template <typename T, int D>
+int launch_decode_typed(const void* q, const void* k, const void* v, float* out, float* m,
+                        float* l, const ra_shape& s, int sk_eff, long long kv_head_stride,
+                        void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  using C = DecodeCfg<T, D>;
+  const int kvH = kv_heads_of(s);
+  const Plan p = make_plan(s.batch, s.heads, kvH, sk_eff, C::kRowsPerStage, sm_count());
+  const size_t prow = static_cast<size_t>(p.n_split) * s.batch * s.heads;
+  const size_t need = prow * (D + 2) * sizeof(float);
+  if (workspace == nullptr) {
+    const int rc = ensure_workspace(need, &workspace);
+    if (rc != RA_OK) return rc;
+  } else {
+    RAB_REQUIRE(workspace_bytes >= need, RA_ERR_OVERFLOW,
+                "decode workspace too small: %zu < %zu bytes", workspace_bytes, need);
+  }
+  float* Mp = static_cast<float*>(workspace);
+  float* Lp = Mp + prow;
+  float* Op = Lp + prow;
+  const float scale_log2 = kLog2e / sqrtf(static_cast<float>(D));
+  const dim3 grid(p.n_split, kvH * p.head_batches, s.batch);
+  const size_t red_bytes = static_cast<size_t>(kWarps) * 8 * (D + 2) * sizeof(float);
+  const size_t smem = std::max(static_cast<size_t>(C::kSmemBytes), red_bytes);
+#define RAB_DECODE_GB(GBV)                                                                     \
+  case GBV: {                                                                                  \
+    auto kern = decode_split_kernel<T, D, GBV>;                                                \
+    RAB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                  static_cast<int>(smem)));                                    \
+    kern<<<grid, kThreads, smem, stream>>>(static_cast<const T*>(q), static_cast<const T*>(k), \
+                                           static_cast<const T*>(v), Mp, Lp, Op, s.batch,      \
+                                           s.heads, kvH, sk_eff, kv_head_stride,               \
+                                           p.rows_per_split, p.head_batches, scale_log2);      \
+  } break;
+  switch (p.gb) {
+    RAB_DECODE_GB(1)
+    RAB_DECODE_GB(2)
+    RAB_DECODE_GB(4)
+    RAB_DECODE_GB(8)
+  }
+#undef RAB_DECODE_GB
+  RAB_CUDA(cudaGetLastError());
+  decode_reduce_kernel<<<dim3(s.heads, s.batch), D, 0, stream>>>(Mp, Lp, Op, m, l, out, s.batch,
+                                                                 s.heads, D, p.n_split);
+  RAB_CUDA(cudaGetLastError());
+  return RA_OK;
+}
+
+template <typename T>
+int launch_decode_dtype(const void* q, const void* k, const void* v, float* out, float* m,
+                        float* l, const ra_shape& s, int sk_eff, long long kv_head_stride,
+                        void* ws, size_t ws_bytes, cudaStream_t stream) {
+  switch (s.head_dim) {
+    case 32:
+      return launch_decode_typed<T, 32>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
+                                        ws_bytes, stream);
+    case 64:
+      return launch_decode_typed<T, 64>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
+                                        ws_bytes, stream);
+    case 128:
+      return launch_decode_typed<T, 128>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
+                                         ws_bytes, stream);
+    case 256:
+      return launch_decode_typed<T, 256>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
+                                         ws_bytes, stream);
+  }
+  set_error("attention_decode_step: unsupported head_dim=%d (supported: 32, 64, 128, 256)",
+            s.head_dim);
+  return RA_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+int decode_step(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
+                float* l, const ra_shape& s, int q_offset, int k_offset, int causal,
+                cudaStream_t stream, int kv_row_stride, void* ws, size_t ws_bytes) {
+  RAB_REQUIRE(q && k && v && out && m && l, RA_ERR_INVALID, "decode step: null argument");
+  RAB_REQUIRE(s.seq_q == 1, RA_ERR_INVALID, "decode step: seq_q must be 1 (got %d)", s.seq_q);
+  RAB_REQUIRE(s.batch > 0 && s.heads > 0 && s.batch <= 65535, RA_ERR_INVALID,
+              "decode step: bad batch/heads");
+  RAB_REQUIRE((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+               reinterpret_cast<uintptr_t>(v)) % 16 == 0,
+              RA_ERR_INVALID, "decode step: q, k and v must be 16-byte aligned");
+  int sk_eff = s.seq_k;
+  if (causal) {
+    // rows [0, q_offset - k_offset] are visible (reference: src/attention_decode.cu:110-116)
+    const long long vis = static_cast<long long>(q_offset) - k_offset + 1;
+    if (vis < sk_eff) sk_eff = vis < 0 ? 0 : static_cast<int>(vis);
+  }
+  if (sk_eff <= 0) return RA_OK;  // nothing visible: the state stays as it is
+  const int stride_rows = kv_row_stride > 0 ? kv_row_stride : s.seq_k;
+  const long long kv_head_stride = static_cast<long long>(stride_rows) * s.head_dim;
+  switch (dtype) {
+    case RA_F32:
+      return launch_decode_dtype<float>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
+                                        ws_bytes, stream);
+    case RA_F16:
+      return launch_decode_dtype<__half>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
+                                         ws_bytes, stream);
+    case RA_BF16:
+      return launch_decode_dtype<__nv_bfloat16>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
+                                                ws_bytes, stream);
+  }
+  set_error("decode step: unknown dtype %d", dtype);
+  return RA_ERR_INVALID;
+}
+
+}  // namespace rab
+
+extern "C" {
+
+size_t ra_decode_workspace_bytes(const ra_shape* shape) {
+  if (!shape) return 0;
+  return static_cast<size_t>(rab::kMaxSplits) * shape->batch * shape->heads *
+         (static_cast<size_t>(shape->head_dim) + 2) * sizeof(float);
+}
+
+int ra_attention_decode_step(int dtype, const void* q, const void* k, const void* v, float* out,
+                             float* m, float* l, const ra_shape* shape, int q_offset, int k_offset,
+                             int causal, ra_stream stream, int kv_row_stride, void* workspace,
+                             size_t workspace_bytes) {
+  RAB_REQUIRE(shape != nullptr, RA_ERR_INVALID, "ra_attention_decode_step: null shape");
+  return rab::decode_step(dtype, q, k, v, out, m, l, *shape, q_offset, k_offset, causal,
+                          static_cast<cudaStream_t>(stream), kv_row_stride, workspace,
+                          workspace_bytes);
+}
+
+}  // extern "C"

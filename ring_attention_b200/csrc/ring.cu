@@ -1,0 +1,377 @@
+// Multi-GPU drivers: the overlapped ring prefill pass and the all-gather decode step, one
+// rank per GPU over NCCL (NVLink 5 / NVSwitch inside one box).
+//
+// Prefill replaces run_ring_overlap_fp16 (src/ring_loop_fp16.cu:522-818) with three changes
+// that matter on this hardware: the communicator lives as long as the ring handle instead of
+// being rebuilt per run (src/ring_loop_fp16.cu:587), a ring step is ONE kernel launch over
+// the whole shard (segment maps) instead of n_seg^2 launches (src/ring_loop_fp16.cu:642-655),
+// and init / finalize are folded into the first / last step's epilogue. The rotation itself
+// is the reference's: ncclSend to rank+1 and ncclRecv from rank-1 in one group on a side
+// stream, double-buffered in local HBM, with an event fence so a buffer is not overwritten
+// while the previous step still reads it (src/ring_loop_fp16.cu:658-701).
+//
+// Decode replaces run_ring_decode_step (src/ring_decode.cu:85-226): the local partial is
+// computed straight into the all-gather send buffer (no pack copies), one ncclAllGather of
+// B*H*(D+2) floats per rank, then merge + normalise in one kernel.
+//
+// NCCL is loaded with dlopen at ring creation, so the rest of the library works without it.
+#include <dlfcn.h>
+
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace rab {
+namespace {
+
+typedef struct ncclComm* ncclComm_t;
+struct NcclId {
+  char internal[128];
+};
+enum { kNcclInt8 = 0, kNcclFloat = 7 };
+
+struct Nccl {
+  void* handle = nullptr;
+  int (*GetUniqueId)(NcclId*) = nullptr;
+  int (*CommInitRank)(ncclComm_t*, int, NcclId, int) = nullptr;
+  int (*CommDestroy)(ncclComm_t) = nullptr;
+  int (*Send)(const void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*Recv)(void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+};
+
+Nccl g_nccl;
+std::once_flag g_nccl_once;
+
+bool load_nccl() {
+  std::call_once(g_nccl_once, []() {
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+      g_nccl.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+      if (g_nccl.handle) break;
+    }
+    if (!g_nccl.handle) return;
+    void* h = g_nccl.handle;
+    g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+    g_nccl.CommInitRank =
+        reinterpret_cast<decltype(g_nccl.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+    g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+    g_nccl.Send = reinterpret_cast<decltype(g_nccl.Send)>(dlsym(h, "ncclSend"));
+    g_nccl.Recv = reinterpret_cast<decltype(g_nccl.Recv)>(dlsym(h, "ncclRecv"));
+    g_nccl.AllGather = reinterpret_cast<decltype(g_nccl.AllGather)>(dlsym(h, "ncclAllGather"));
+    g_nccl.GroupStart = reinterpret_cast<decltype(g_nccl.GroupStart)>(dlsym(h, "ncclGroupStart"));
+    g_nccl.GroupEnd = reinterpret_cast<decltype(g_nccl.GroupEnd)>(dlsym(h, "ncclGroupEnd"));
+    g_nccl.GetErrorString =
+        reinterpret_cast<decltype(g_nccl.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+  });
+  return g_nccl.handle && g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy &&
+         g_nccl.Send && g_nccl.Recv && g_nccl.AllGather && g_nccl.GroupStart && g_nccl.GroupEnd;
+}
+
+#define RAB_NCCL(expr)                                                                      \
+  do {                                                                                      \
+    int _r = (expr);                                                                        \
+    if (_r != 0) {                                                                          \
+      ::rab::set_error("NCCL error %d (%s) at %s:%d in %s", _r,                             \
+                       g_nccl.GetErrorString ? g_nccl.GetErrorString(_r) : "?", __FILE__,   \
+                       __LINE__, #expr);                                                    \
+      return RA_ERR_NCCL;                                                                   \
+    }                                                                                       \
+  } while (0)
+
+constexpr int kMaxRanks = 64;
+
+}  // namespace
+}  // namespace rab
+
+using namespace rab;
+
+struct ra_ring {
+  int rank, cp;
+  ncclComm_t comm;
+  bool own_comm;
+  cudaStream_t comm_stream;
+  cudaEvent_t ev_start, ev_end;
+  cudaEvent_t ev_comm[kMaxRanks], ev_comm_begin[kMaxRanks];
+  cudaEvent_t ev_comp[kMaxRanks], ev_comp_begin[kMaxRanks];
+  // decode buffers, grown on demand: send [O|m|l] block and cp * block receive area
+  float* dec_buf;
+  size_t dec_bytes;
+};
+
+static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+static int ring_finish_create(int rank, int cp, ncclComm_t comm, bool own, ra_ring** out) {
+  ra_ring* r = new ra_ring();
+  r->rank = rank;
+  r->cp = cp;
+  r->comm = comm;
+  r->own_comm = own;
+  r->dec_buf = nullptr;
+  r->dec_bytes = 0;
+  RAB_CUDA(cudaStreamCreateWithFlags(&r->comm_stream, cudaStreamNonBlocking));
+  RAB_CUDA(cudaEventCreate(&r->ev_start));
+  RAB_CUDA(cudaEventCreate(&r->ev_end));
+  for (int i = 0; i < kMaxRanks; ++i) {
+    RAB_CUDA(cudaEventCreate(&r->ev_comm[i]));
+    RAB_CUDA(cudaEventCreate(&r->ev_comm_begin[i]));
+    RAB_CUDA(cudaEventCreate(&r->ev_comp[i]));
+    RAB_CUDA(cudaEventCreate(&r->ev_comp_begin[i]));
+  }
+  *out = r;
+  return RA_OK;
+}
+
+extern "C" {
+
+int ra_nccl_unique_id(char id[128]) {
+  RAB_REQUIRE(id != nullptr, RA_ERR_INVALID, "ra_nccl_unique_id: null argument");
+  RAB_REQUIRE(load_nccl(), RA_ERR_NCCL, "libnccl.so.2 could not be loaded: %s", dlerror());
+  NcclId nid;
+  RAB_NCCL(g_nccl.GetUniqueId(&nid));
+  std::memcpy(id, nid.internal, 128);
+  return RA_OK;
+}
+
+int ra_ring_create(int rank, int cp_size, const char id[128], ra_ring** out) {
+  RAB_REQUIRE(out != nullptr, RA_ERR_INVALID, "ra_ring_create: null argument");
+  RAB_REQUIRE(cp_size >= 1 && cp_size <= kMaxRanks && rank >= 0 && rank < cp_size, RA_ERR_INVALID,
+              "ra_ring_create: bad rank %d / cp_size %d", rank, cp_size);
+  ncclComm_t comm = nullptr;
+  if (cp_size > 1) {
+    RAB_REQUIRE(id != nullptr, RA_ERR_INVALID, "ra_ring_create: null unique id");
+    RAB_REQUIRE(load_nccl(), RA_ERR_NCCL, "libnccl.so.2 could not be loaded: %s", dlerror());
+    NcclId nid;
+    std::memcpy(nid.internal, id, 128);
+    RAB_NCCL(g_nccl.CommInitRank(&comm, cp_size, nid, rank));
+  }
+  return ring_finish_create(rank, cp_size, comm, true, out);
+}
+
+int ra_ring_create_from_comm(int rank, int cp_size, void* nccl_comm, ra_ring** out) {
+  RAB_REQUIRE(out != nullptr, RA_ERR_INVALID, "ra_ring_create_from_comm: null argument");
+  RAB_REQUIRE(cp_size >= 1 && cp_size <= kMaxRanks && rank >= 0 && rank < cp_size, RA_ERR_INVALID,
+              "ra_ring_create_from_comm: bad rank %d / cp_size %d", rank, cp_size);
+  if (cp_size > 1) {
+    RAB_REQUIRE(nccl_comm != nullptr, RA_ERR_INVALID, "ra_ring_create_from_comm: null comm");
+    RAB_REQUIRE(load_nccl(), RA_ERR_NCCL, "libnccl.so.2 could not be loaded: %s", dlerror());
+  }
+  return ring_finish_create(rank, cp_size, static_cast<ncclComm_t>(nccl_comm), false, out);
+}
+
+void ra_ring_destroy(ra_ring* r) {
+  if (!r) return;
+  cudaStreamSynchronize(r->comm_stream);
+  if (r->comm && r->own_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(r->comm);
+  cudaStreamDestroy(r->comm_stream);
+  cudaEventDestroy(r->ev_start);
+  cudaEventDestroy(r->ev_end);
+  for (int i = 0; i < kMaxRanks; ++i) {
+    cudaEventDestroy(r->ev_comm[i]);
+    cudaEventDestroy(r->ev_comm_begin[i]);
+    cudaEventDestroy(r->ev_comp[i]);
+    cudaEventDestroy(r->ev_comp_begin[i]);
+  }
+  if (r->dec_buf) cudaFree(r->dec_buf);
+  delete r;
+}
+
+static int check_cfg(const ra_ring* r, const ra_ring_config* c) {
+  RAB_REQUIRE(r && c, RA_ERR_INVALID, "ring prefill: null argument");
+  RAB_REQUIRE(c->dtype == RA_F16 || c->dtype == RA_BF16 || c->dtype == RA_F32, RA_ERR_INVALID,
+              "ring prefill: unknown dtype %d", c->dtype);
+  RAB_REQUIRE(c->batch > 0 && c->heads > 0 && c->seq > 0, RA_ERR_INVALID,
+              "ring prefill: bad shape");
+  RAB_REQUIRE(c->layout >= 0 && c->layout <= 2, RA_ERR_INVALID, "ring prefill: bad layout %d",
+              c->layout);
+  // the reference's validation (src/ring_loop.cu:1584-1593, src/ring_partition.cpp:43-49)
+  RAB_REQUIRE(c->seq % r->cp == 0, RA_ERR_INVALID, "seq=%d must be divisible by cp_size=%d",
+              c->seq, r->cp);
+  if (c->layout == 1) {
+    RAB_REQUIRE(c->n_splits >= 2 && c->n_splits <= RA_MAX_SEG, RA_ERR_INVALID,
+                "zig-zag needs 2 <= n_splits <= %d (got %d)", RA_MAX_SEG, c->n_splits);
+    RAB_REQUIRE(c->seq % (c->n_splits * r->cp) == 0, RA_ERR_INVALID,
+                "seq=%d must be divisible by n_splits*cp_size=%d", c->seq, c->n_splits * r->cp);
+  }
+  return RA_OK;
+}
+
+size_t ra_ring_prefill_workspace_bytes(const ra_ring* r, const ra_ring_config* c) {
+  if (!r || !c || r->cp <= 0) return 0;
+  const int kvH = c->kv_heads > 0 ? c->kv_heads : c->heads;
+  const size_t es = c->dtype == RA_F32 ? 4 : 2;
+  const size_t sloc = static_cast<size_t>(c->seq / r->cp);
+  const size_t kv_bytes = align256(static_cast<size_t>(c->batch) * kvH * sloc * c->head_dim * es);
+  const size_t ml = align256(static_cast<size_t>(c->batch) * c->heads * sloc * sizeof(float));
+  return (r->cp > 1 ? 4 * kv_bytes : 0) + 2 * ml + 256;
+}
+
+int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const void* k,
+                    const void* v, float* out, float* lse, void* kv_work, size_t kv_work_bytes,
+                    ra_stream stream_, ra_ring_result* result) {
+  int rc = check_cfg(r, c);
+  if (rc != RA_OK) return rc;
+  RAB_REQUIRE(q && k && v && out && kv_work, RA_ERR_INVALID, "ring prefill: null argument");
+  RAB_REQUIRE(kv_work_bytes >= ra_ring_prefill_workspace_bytes(r, c), RA_ERR_OVERFLOW,
+              "ring prefill: workspace too small");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int P = r->cp;
+  const int kvH = c->kv_heads > 0 ? c->kv_heads : c->heads;
+  const size_t es = c->dtype == RA_F32 ? 4 : 2;
+  const int sloc = c->seq / P;
+  const size_t kv_raw = static_cast<size_t>(c->batch) * kvH * sloc * c->head_dim * es;
+  const size_t kv_bytes = align256(kv_raw);
+  const size_t rows = static_cast<size_t>(c->batch) * c->heads * sloc;
+  unsigned char* base = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(kv_work) + 255) & ~static_cast<uintptr_t>(255));
+  unsigned char* buf_k[2] = {nullptr, nullptr};
+  unsigned char* buf_v[2] = {nullptr, nullptr};
+  if (P > 1) {
+    buf_k[0] = base;
+    buf_v[0] = base + kv_bytes;
+    buf_k[1] = base + 2 * kv_bytes;
+    buf_v[1] = base + 3 * kv_bytes;
+    base += 4 * kv_bytes;
+  }
+  float* m = reinterpret_cast<float*>(base);
+  float* l = reinterpret_cast<float*>(base + align256(rows * sizeof(float)));
+
+  ra_shape shape{c->batch, c->heads, sloc, sloc, c->head_dim, kvH};
+  const int next = (r->rank + 1) % P, prev = (r->rank - 1 + P) % P;
+
+  RAB_CUDA(cudaEventRecord(r->ev_start, stream));
+  RAB_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_start, 0));
+  for (int s = 0; s < P; ++s) {
+    const void* cur_k = s == 0 ? k : buf_k[(s - 1) & 1];
+    const void* cur_v = s == 0 ? v : buf_v[(s - 1) & 1];
+    if (s < P - 1) {
+      // the buffer about to be received into was the source of compute step s-1
+      if (s >= 1) RAB_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_comp[s - 1], 0));
+      RAB_CUDA(cudaEventRecord(r->ev_comm_begin[s], r->comm_stream));
+      RAB_NCCL(g_nccl.GroupStart());
+      RAB_NCCL(g_nccl.Send(cur_k, kv_raw, kNcclInt8, next, r->comm, r->comm_stream));
+      RAB_NCCL(g_nccl.Recv(buf_k[s & 1], kv_raw, kNcclInt8, prev, r->comm, r->comm_stream));
+      RAB_NCCL(g_nccl.Send(cur_v, kv_raw, kNcclInt8, next, r->comm, r->comm_stream));
+      RAB_NCCL(g_nccl.Recv(buf_v[s & 1], kv_raw, kNcclInt8, prev, r->comm, r->comm_stream));
+      RAB_NCCL(g_nccl.GroupEnd());
+      RAB_CUDA(cudaEventRecord(r->ev_comm[s], r->comm_stream));
+    }
+    if (s > 0) RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[s - 1], 0));
+    ra_segmap qmap, kmap;
+    const int stride =
+        ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s, &qmap, &kmap);
+    RAB_REQUIRE(stride >= 1, RA_ERR_INVALID, "ring prefill: bad partition");
+    unsigned flags = c->causal ? RA_STEP_CAUSAL : 0u;
+    if (s == 0) flags |= RA_STEP_FRESH;
+    if (s == P - 1) flags |= RA_STEP_FINALIZE;
+    RAB_CUDA(cudaEventRecord(r->ev_comp_begin[s], stream));
+    rc = ra_attention_step_ex(c->dtype, q, cur_k, cur_v, out, m, l, &shape, &qmap, &kmap, stride,
+                              flags, c->doc_len, 0, stream);
+    if (rc != RA_OK) return rc;
+    RAB_CUDA(cudaEventRecord(r->ev_comp[s], stream));
+  }
+  if (lse) {
+    rc = ra_attention_lse(m, l, lse, rows, stream);
+    if (rc != RA_OK) return rc;
+  }
+  RAB_CUDA(cudaEventRecord(r->ev_end, stream));
+  if (result) {
+    RAB_CUDA(cudaStreamSynchronize(stream));
+    RAB_CUDA(cudaStreamSynchronize(r->comm_stream));
+    float ms = 0.f;
+    double comp = 0.0, comm = 0.0;
+    for (int s = 0; s < P; ++s) {
+      RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_comp_begin[s], r->ev_comp[s]));
+      comp += ms;
+      if (s < P - 1) {
+        RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_comm_begin[s], r->ev_comm[s]));
+        comm += ms;
+      }
+    }
+    RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_start, r->ev_end));
+    result->total_ms = ms;
+    result->comp_ms = comp;
+    result->comm_ms = comm;
+    // time the compute stream spent not computing: transfers that were not hidden
+    result->wait_ms = ms - comp > 0.0 ? ms - comp : 0.0;
+  }
+  return RA_OK;
+}
+
+int ra_ring_decode_step(ra_ring* r, int batch, int heads, const void* q, const void* k_new,
+                        const void* v_new, int owner_rank, ra_kv_cache* cache,
+                        const int* current_len_per_rank, float* out, ra_stream stream_,
+                        ra_ring_result* result) {
+  RAB_REQUIRE(r && q && cache && current_len_per_rank && out, RA_ERR_INVALID,
+              "ring decode: null argument");
+  RAB_REQUIRE(owner_rank >= 0 && owner_rank < r->cp, RA_ERR_INVALID,
+              "ring decode: owner_rank %d out of range", owner_rank);
+  RAB_REQUIRE(batch == cache->batch, RA_ERR_INVALID, "ring decode: batch %d != cache batch %d",
+              batch, cache->batch);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int D = cache->head_dim;
+  if (r->rank == owner_rank) {
+    RAB_REQUIRE(k_new && v_new, RA_ERR_INVALID, "ring decode: owner needs k_new / v_new");
+    const int rc = ra_kv_cache_append(cache, k_new, v_new, stream_);
+    if (rc != RA_OK) return rc;
+  }
+  // the caller's bookkeeping must agree with the cache (src/ring_decode.cu:108-125)
+  RAB_REQUIRE(current_len_per_rank[r->rank] == cache->current_len, RA_ERR_INVALID,
+              "ring_decode: current_len_per_rank[%d]=%d but cache.current_len=%d", r->rank,
+              current_len_per_rank[r->rank], cache->current_len);
+  const size_t bh = static_cast<size_t>(batch) * heads;
+  const size_t block = bh * D + 2 * bh;  // floats per rank: [O | m | l]
+  const size_t need = (1 + static_cast<size_t>(r->cp)) * block * sizeof(float);
+  if (r->dec_bytes < need) {
+    if (r->dec_buf) RAB_CUDA(cudaFree(r->dec_buf));
+    r->dec_buf = nullptr;
+    r->dec_bytes = 0;
+    RAB_CUDA(cudaMalloc(reinterpret_cast<void**>(&r->dec_buf), need));
+    r->dec_bytes = need;
+  }
+  float* send = r->dec_buf;
+  float* recv = r->dec_buf + block;
+  float* o_p = send;
+  float* m_p = send + bh * D;
+  float* l_p = m_p + bh;
+  RAB_CUDA(cudaEventRecord(r->ev_start, stream));
+  int rc = launch_init(o_p, m_p, l_p, bh * D, bh, stream);
+  if (rc != RA_OK) return rc;
+  const int local_len = cache->current_len;
+  if (local_len > 0) {
+    ra_shape s{batch, heads, 1, local_len, D, cache->kv_heads};
+    // causality is implicit: the cache only ever holds past tokens (src/ring_decode.cu:173-175)
+    rc = decode_step(cache->dtype, q, cache->k, cache->v, o_p, m_p, l_p, s, 0, 0, 0, stream,
+                     cache->s_max, nullptr, 0);
+    if (rc != RA_OK) return rc;
+  }
+  RAB_CUDA(cudaEventRecord(r->ev_comp[0], stream));
+  const float* gathered = send;
+  if (r->cp > 1) {
+    RAB_NCCL(g_nccl.AllGather(send, recv, block, kNcclFloat, r->comm, stream));
+    gathered = recv;
+  }
+  RAB_CUDA(cudaEventRecord(r->ev_comm[0], stream));
+  rc = ra_decode_partial_merge(gathered, out, nullptr, nullptr, r->cp, static_cast<int>(bh), D, 1,
+                               stream_);
+  if (rc != RA_OK) return rc;
+  RAB_CUDA(cudaEventRecord(r->ev_end, stream));
+  if (result) {
+    RAB_CUDA(cudaStreamSynchronize(stream));
+    float a = 0.f, b = 0.f, t = 0.f;
+    RAB_CUDA(cudaEventElapsedTime(&a, r->ev_start, r->ev_comp[0]));
+    RAB_CUDA(cudaEventElapsedTime(&b, r->ev_comp[0], r->ev_comm[0]));
+    RAB_CUDA(cudaEventElapsedTime(&t, r->ev_start, r->ev_end));
+    result->comp_ms = a;
+    result->comm_ms = b;
+    result->wait_ms = b;
+    result->total_ms = t;
+  }
+  return RA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,798 @@
+// Blackwell (sm_100a) ring step for fp16 / bf16 Q/K/V: a FlashAttention-style forward built
+// directly on TMA, tcgen05.mma and tensor memory. Replaces the reference's one-warp wmma
+// kernel (src/attention_step_fp16.cu:41-212) and, because positions come from segment
+// maps, also the n_seg^2 launches per ring step of its driver
+// (src/ring_loop_fp16.cu:642-655): one launch covers a whole zig-zag shard and skips the
+// K tiles no row of the block can see.
+//
+// Work decomposition
+//   grid = (batch * heads, query blocks). A block owns 256 query rows of one segment as two
+//   128-row tiles and walks the visible 128-key tiles of every key segment.
+//   Heaviest query blocks (largest positions) are launched first.
+//
+// Roles inside a block (384 threads)
+//   warp 0        TMA producer: Q tiles once, then K_j, V_j, K_j+1, ... into a shared-memory
+//                 ring of 128B-swizzled tiles (cp.async.bulk.tensor, no multicast).
+//   warp 1        MMA issuer (one lane): S_w = Q_w K_j^T and O_w += P_w V_j with fp32
+//                 accumulators in tensor memory; also allocates / frees tensor memory.
+//   warps 4-7     softmax for query tile 0: one thread per row reads S from tensor memory,
+//   warps 8-11    (tile 1) keeps the running max / sum, writes P as 16-bit back into tensor
+//                 memory (over S) or into shared memory, rescales O only when the row
+//                 maximum moved by more than 2^8, and runs the epilogue.
+//   The two query tiles ping-pong: while one tile's rows are in softmax the tensor core
+//   works on the other tile.
+//
+// Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+//
+// Epilogue: the step's partial (O, m, l) is merged with the persistent state in HBM using
+// the log-sum-exp merge, which is the same recurrence as folding the tiles one by one
+// (src/attention_step_fp16.cu:155-172), so the (out, m, l) contract of the reference holds:
+// unnormalised out, natural-log m, rows without a visible key untouched.
+//
+// Every wait on an mbarrier is bounded: when one runs out the block records where in the
+// device status word, all roles leave their loops, tensor memory is freed and the kernel
+// returns; later blocks see the status word and return at once.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace rab {
+
+namespace {
+
+constexpr int kThreads = 384;
+constexpr int kBM = 128;           // query rows per tile (two tiles per block)
+constexpr int kBN = 128;           // keys per tile
+constexpr int kQBlock = 2 * kBM;   // query rows per block
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O when the max moved > 2^8
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+
+// ---- PTX wrappers -------------------------------------------------------------------
+__device__ inline unsigned smem_u32(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ inline void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ inline void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ inline void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ inline bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ inline unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait. Returns false when the block is aborting (own limit reached or another
+// role flagged it). `which` identifies the wait in the status word.
+__device__ inline bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag,
+                                 int* status, int which, int tile) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  unsigned spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (atomicCAS(&status[0], 0, RA_ERR_DEVICE_WAIT) == 0) {
+          status[1] = which;
+          status[2] = static_cast<int>(blockIdx.x + blockIdx.y * gridDim.x);
+          status[3] = tile;
+        }
+        return false;
+      }
+    }
+  }
+}
+
+__device__ inline void tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0,
+                                   int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ inline void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ inline void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ inline void tc_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ inline void mma_ss(unsigned d_tmem, unsigned long long a_desc,
+                              unsigned long long b_desc, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ inline void mma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc,
+                              unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ inline void tmem_ld32(unsigned taddr, float (&r)[32]) {
+  unsigned u[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"  // same statement: no use of the registers can move above it
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]),
+        "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]),
+        "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]),
+        "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]),
+        "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
+}
+__device__ inline void tmem_st32(unsigned taddr, const float (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
+          taddr),
+      "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])),
+      "r"(__float_as_uint(r[3])), "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])),
+      "r"(__float_as_uint(r[6])), "r"(__float_as_uint(r[7])), "r"(__float_as_uint(r[8])),
+      "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])), "r"(__float_as_uint(r[11])),
+      "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])),
+      "r"(__float_as_uint(r[15])), "r"(__float_as_uint(r[16])), "r"(__float_as_uint(r[17])),
+      "r"(__float_as_uint(r[18])), "r"(__float_as_uint(r[19])), "r"(__float_as_uint(r[20])),
+      "r"(__float_as_uint(r[21])), "r"(__float_as_uint(r[22])), "r"(__float_as_uint(r[23])),
+      "r"(__float_as_uint(r[24])), "r"(__float_as_uint(r[25])), "r"(__float_as_uint(r[26])),
+      "r"(__float_as_uint(r[27])), "r"(__float_as_uint(r[28])), "r"(__float_as_uint(r[29])),
+      "r"(__float_as_uint(r[30])), "r"(__float_as_uint(r[31]))
+      : "memory");
+}
+__device__ inline void tmem_st16(unsigned taddr, const unsigned (&u)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+      "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15])
+      : "memory");
+}
+__device__ inline void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ inline float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Shared-memory matrix descriptors for 128B-swizzled tiles (8-row groups 1024 B apart).
+// K-major operand (rows = M or N index, 64 contiguous 16-bit elements of the contraction
+// dimension per 128-byte row); the leading byte offset is unused for swizzled K-major.
+__device__ inline unsigned long long desc_kmajor(unsigned saddr) {
+  const unsigned lo = ((saddr & 0x3FFFFu) >> 4) | (1u << 16);
+  const unsigned hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO, version 1, SWIZZLE_128B
+  return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+// MN-major operand (rows = contraction index, 64 contiguous elements of N per 128-byte row):
+// leading byte offset = distance between 64-element N blocks, stride = between 8-row groups.
+__device__ inline unsigned long long desc_mnmajor(unsigned saddr, unsigned lbo_bytes) {
+  const unsigned lo = ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+  const unsigned hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, A/B format (0 fp16, 1 bf16), A K-major,
+// B K-major (b_mn = 0) or MN-major (1), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr unsigned make_idesc(unsigned fmt, unsigned b_mn, unsigned n,
+                                                  unsigned m) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((n >> 3) << 17) |
+         ((m >> 4) << 24);
+}
+
+template <int D, bool kPInTmem>
+struct TcCfg {
+  static constexpr int kTileBytes = kBM * D * 2;  // one 128-row tile of Q, K or V
+  static constexpr int kBoxes = D / 64;           // 64-element (128-byte) boxes per tile
+  static constexpr int kStages = kPInTmem ? (D == 128 ? 4 : 6) : (D == 128 ? 3 : 6);
+  static constexpr int kPBytes = kPInTmem ? 0 : kBM * kBN * 2;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffKV = 2 * kTileBytes;
+  static constexpr int kOffP = kOffKV + kStages * kTileBytes;
+  static constexpr int kOffBar = kOffP + 2 * kPBytes;
+  static constexpr int kNumBars = 2 + 2 * kStages + 6;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + alignment slack
+  static constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
+};
+
+struct TileRange {
+  int lo, hi;  // key tiles [lo, hi) of a segment that some row of the block can see
+};
+
+// Visible key-tile range of key segment `sk` for a query block whose rows span positions
+// [qmin, qmax] (both ends are positions of real rows).
+__device__ inline TileRange tile_range(const PosMap& kmap, int sk, int stride, bool causal,
+                                       long long doc_len, int qmin, int qmax) {
+  const int L = kmap.seg_len;
+  const long long kb = kmap.base[sk];
+  long long j_lo = 0, j_hi = L - 1;  // visible local key indices, inclusive
+  if (causal) {
+    const long long d = static_cast<long long>(qmax) - kb;
+    if (d < 0) return {0, 0};
+    j_hi = min(j_hi, d / stride);
+  }
+  if (doc_len > 0) {
+    const long long p_lo = (static_cast<long long>(qmin) / doc_len) * doc_len;
+    const long long p_hi = (static_cast<long long>(qmax) / doc_len + 1) * doc_len - 1;
+    if (p_hi < kb) return {0, 0};
+    j_hi = min(j_hi, (p_hi - kb) / stride);
+    if (p_lo > kb) j_lo = (p_lo - kb + stride - 1) / stride;
+  }
+  if (j_hi < j_lo) return {0, 0};
+  return {static_cast<int>(j_lo / kBN), static_cast<int>(j_hi / kBN) + 1};
+}
+
+struct TcArgs {
+  float* out;
+  float* m;
+  float* l;
+  int H, kvH, Sq;
+  int n_qblocks_per_seg;
+  PosMap qmap, kmap;
+  int stride;
+  unsigned flags;
+  long long doc_len;
+  int* status;
+};
+
+template <int D, bool kBf16, bool kPInTmem>
+__global__ void __launch_bounds__(kThreads, 1)
+    step_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const TcArgs a) {
+  using C = TcCfg<D, kPInTmem>;
+  extern __shared__ unsigned char smem_raw[];
+  // 128B-swizzled tiles need 1024-byte alignment
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const unsigned s_base = smem_u32(smem);
+  const unsigned s_q = s_base + C::kOffQ;
+  const unsigned s_kv = s_base + C::kOffKV;
+  const unsigned s_p = s_base + C::kOffP;
+  const unsigned s_bar = s_base + C::kOffBar;
+  // barrier table
+  const unsigned bar_q_full = s_bar;                            // [2]
+  const unsigned bar_kv_full = s_bar + 16;                      // [kStages]
+  const unsigned bar_kv_empty = bar_kv_full + 8 * C::kStages;   // [kStages]
+  const unsigned bar_s_full = bar_kv_empty + 8 * C::kStages;    // [2]
+  const unsigned bar_p_full = bar_s_full + 16;                  // [2]
+  const unsigned bar_o_done = bar_p_full + 16;                  // [2]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + C::kOffBar + C::kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // An earlier block gave up: leave at once (the vote makes the decision block-uniform).
+  if (__syncthreads_or(*reinterpret_cast<volatile int*>(a.status) != 0)) return;
+
+  const bool causal = (a.flags & RA_STEP_CAUSAL) != 0;
+  const bool fresh = (a.flags & RA_STEP_FRESH) != 0;
+  const bool finalize = (a.flags & RA_STEP_FINALIZE) != 0;
+
+  // Block -> (batch*head, query segment, 256-row block inside the segment); heavy first.
+  const int bh = blockIdx.x;
+  const int qb_lin = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
+  const int sq = qb_lin / a.n_qblocks_per_seg;
+  const int tq = qb_lin - sq * a.n_qblocks_per_seg;
+  const int h = bh % a.H;
+  const int b = bh / a.H;
+  const int kv_bh = b * a.kvH + (h % a.kvH);
+  const int q_seg_len = a.qmap.seg_len;
+  const int row0 = tq * kQBlock;  // first row of the block inside its segment
+  const int rows_in_block = min(kQBlock, q_seg_len - row0);
+  const int qmin = a.qmap.base[sq] + row0 * a.stride;
+  const int qmax = a.qmap.base[sq] + (row0 + rows_in_block - 1) * a.stride;
+
+  // Tile list: segments in order, tiles [lo, hi) of each; identical in every role.
+  int n_tiles = 0;
+  for (int sk = 0; sk < a.kmap.n_seg; ++sk) {
+    const TileRange r = tile_range(a.kmap, sk, a.stride, causal, a.doc_len, qmin, qmax);
+    n_tiles += r.hi - r.lo;
+  }
+
+  if (tid == 0) {
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_full + 8, 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_kv_full + 8 * s, 1);
+      mbar_init(bar_kv_empty + 8 * s, 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(bar_s_full + 8 * w, 1);
+      mbar_init(bar_p_full + 8 * w, kBM);
+      mbar_init(bar_o_done + 8 * w, 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(
+                     smem_u32(tmem_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer ----
+    if (lane == 0 && n_tiles > 0) {
+      const int q_row = sq * q_seg_len + row0;
+      for (int w = 0; w < 2; ++w) {
+        mbar_expect_tx(bar_q_full + 8 * w, C::kTileBytes);
+        for (int bx = 0; bx < C::kBoxes; ++bx)
+          tma_load_3d(s_q + w * C::kTileBytes + bx * (kBM * 128), &tmap_q, bar_q_full + 8 * w,
+                      bx * 64, q_row + w * kBM, bh);
+      }
+      int it = 0;
+      bool ok = true;
+      for (int sk = 0; sk < a.kmap.n_seg && ok; ++sk) {
+        const TileRange r = tile_range(a.kmap, sk, a.stride, causal, a.doc_len, qmin, qmax);
+        for (int t = r.lo; t < r.hi && ok; ++t) {
+          const int k_row = sk * a.kmap.seg_len + t * kBN;
+          for (int which = 0; which < 2 && ok; ++which, ++it) {
+            const int slot = it % C::kStages;
+            if (it >= C::kStages)
+              ok = mbar_wait(bar_kv_empty + 8 * slot, ((it / C::kStages) + 1) & 1, abort_flag,
+                             a.status, 1, it);
+            if (!ok) break;
+            mbar_expect_tx(bar_kv_full + 8 * slot, C::kTileBytes);
+            const CUtensorMap* map = which == 0 ? &tmap_k : &tmap_v;
+            for (int bx = 0; bx < C::kBoxes; ++bx)
+              tma_load_3d(s_kv + slot * C::kTileBytes + bx * (kBN * 128), map,
+                          bar_kv_full + 8 * slot, bx * 64, k_row, kv_bh);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer ----
+    if (lane == 0 && n_tiles > 0) {
+      constexpr unsigned kFmt = kBf16 ? 1u : 0u;
+      constexpr unsigned idesc_s = make_idesc(kFmt, 0, kBN, kBM);
+      constexpr unsigned idesc_pv = make_idesc(kFmt, 1, D, kBM);
+      const unsigned t_s[2] = {tmem_base + C::kColS0, tmem_base + C::kColS1};
+      const unsigned t_o[2] = {tmem_base + C::kColO0, tmem_base + C::kColO1};
+      auto issue_s = [&](int w, int slot) {
+        const unsigned qa = s_q + w * C::kTileBytes;
+        const unsigned kb = s_kv + slot * C::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const unsigned off = (ks / 4) * (kBM * 128) + (ks % 4) * 32;
+          mma_ss(t_s[w], desc_kmajor(qa + off), desc_kmajor(kb + off), idesc_s, ks > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int w, int slot, bool acc) {
+        const unsigned vb = s_kv + slot * C::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          const unsigned long long bd = desc_mnmajor(vb + ks * 2048, kBN * 128);
+          const unsigned accum = (acc || ks > 0) ? 1u : 0u;
+          if constexpr (kPInTmem) {
+            mma_ts(t_o[w], t_s[w] + ks * 8, bd, idesc_pv, accum);
+          } else {
+            const unsigned pa = s_p + w * C::kPBytes + (ks / 4) * (kBM * 128) + (ks % 4) * 32;
+            mma_ss(t_o[w], desc_kmajor(pa), bd, idesc_pv, accum);
+          }
+        }
+      };
+      bool ok = true;
+      // prologue: S_0(0), S_1(0)
+      ok = mbar_wait(bar_kv_full, 0, abort_flag, a.status, 2, 0);
+      for (int w = 0; w < 2 && ok; ++w) {
+        ok = mbar_wait(bar_q_full + 8 * w, 0, abort_flag, a.status, 3, w);
+        if (!ok) break;
+        tc_fence_after();
+        issue_s(w, 0);
+        tc_commit(bar_s_full + 8 * w);
+      }
+      if (ok) tc_commit(bar_kv_empty);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int it_v = 2 * j + 1, it_k = 2 * j + 2;
+        const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
+        const bool more = j + 1 < n_tiles;
+        ok = mbar_wait(bar_kv_full + 8 * slot_v, (it_v / C::kStages) & 1, abort_flag, a.status, 4,
+                       j);
+        if (ok && more)
+          ok = mbar_wait(bar_kv_full + 8 * slot_k, (it_k / C::kStages) & 1, abort_flag, a.status,
+                         5, j);
+        for (int w = 0; w < 2 && ok; ++w) {
+          ok = mbar_wait(bar_p_full + 8 * w, j & 1, abort_flag, a.status, 6, j);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(w, slot_v, j > 0);
+          if (more) {
+            issue_s(w, slot_k);
+            tc_commit(bar_s_full + 8 * w);
+          } else {
+            tc_commit(bar_o_done + 8 * w);
+          }
+        }
+        if (ok) {
+          tc_commit(bar_kv_empty + 8 * slot_v);
+          if (more) tc_commit(bar_kv_empty + 8 * slot_k);
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ----------------------------------------------------------------- softmax ----
+    const int w = (warp - 4) >> 2;                   // query tile of this warpgroup
+    const int row = ((warp & 3) << 5) + lane;        // row inside the tile = TMEM lane
+    const unsigned lane_base = static_cast<unsigned>((warp & 3) << 5) << 16;
+    const unsigned t_s = tmem_base + lane_base + (w == 0 ? C::kColS0 : C::kColS1);
+    const unsigned t_o = tmem_base + lane_base + (w == 0 ? C::kColO0 : C::kColO1);
+    const int r_in_seg = row0 + w * kBM + row;
+    const bool row_valid = r_in_seg < q_seg_len;
+    const int qpos = a.qmap.base[sq] + r_in_seg * a.stride;
+    const long long qdoc = a.doc_len > 0 ? qpos / a.doc_len : 0;
+    const float scale_log2 = rsqrtf(static_cast<float>(D)) * kLog2e;
+
+    float m_used = -INFINITY;  // reference point of P and O, log2 units
+    float m_true = -INFINITY;  // true running max, log2 units
+    float l_run = 0.f;
+    bool ok = true;
+
+    int j = 0;
+    for (int sk = 0; sk < a.kmap.n_seg && ok; ++sk) {
+      const TileRange tr = tile_range(a.kmap, sk, a.stride, causal, a.doc_len, qmin, qmax);
+      const int k_seg_len = a.kmap.seg_len;
+      for (int t = tr.lo; t < tr.hi && ok; ++t, ++j) {
+        // Visible columns of this row in this tile form an interval [c_lo, c_hi).
+        const long long kpos0 = static_cast<long long>(a.kmap.base[sk]) +
+                                static_cast<long long>(t) * kBN * a.stride;
+        int c_lo = 0, c_hi = min(kBN, k_seg_len - t * kBN);
+        if (causal) {
+          const long long d = static_cast<long long>(qpos) - kpos0;
+          c_hi = d < 0 ? 0 : static_cast<int>(min(static_cast<long long>(c_hi), d / a.stride + 1));
+        }
+        if (a.doc_len > 0) {
+          const long long p_lo = qdoc * a.doc_len, p_hi = p_lo + a.doc_len - 1;
+          if (p_hi < kpos0) {
+            c_hi = 0;
+          } else {
+            c_hi = static_cast<int>(min(static_cast<long long>(c_hi), (p_hi - kpos0) / a.stride + 1));
+            if (p_lo > kpos0)
+              c_lo = static_cast<int>(min(static_cast<long long>(kBN),
+                                          (p_lo - kpos0 + a.stride - 1) / a.stride));
+          }
+        }
+        if (!row_valid) c_hi = 0;
+        if (c_hi < c_lo) c_hi = c_lo;
+        const bool full = __all_sync(0xffffffffu, c_lo == 0 && c_hi == kBN);
+
+        ok = mbar_wait(bar_s_full + 8 * w, j & 1, abort_flag, a.status, 7, j);
+        ok = __all_sync(0xffffffffu, ok);  // the tensor-memory accesses below are warp-collective
+        if (!ok) break;
+        tc_fence_after();
+
+        // pass 1: row maximum over the visible columns
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+          float s[32];
+          tmem_ld32(t_s + c * 32, s);
+          if (full) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = c * 32 + i;
+              if (col >= c_lo && col < c_hi) mx = fmaxf(mx, s[i]);
+            }
+          }
+        }
+        const float tile_max = mx * scale_log2;  // -inf stays -inf (scale > 0)
+        m_true = fmaxf(m_true, tile_max);
+        // Move the reference point only when it is unset or the max moved by more than the
+        // threshold; otherwise P just runs a little above 1 (at most 2^8), which 16-bit P and
+        // the fp32 sums hold without trouble.
+        float alpha = 1.f;
+        bool rescale = false;
+        if (m_true > m_used + kRescaleThreshold || (m_used == -INFINITY && m_true > -INFINITY)) {
+          if (m_used > -INFINITY) {
+            alpha = ex2(m_used - m_true);
+            rescale = true;
+          }
+          m_used = m_true;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+          // O_w is stable here: S_w(j) was issued after PV_w(j-1) and has completed.
+          l_run *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            float o[32];
+            tmem_ld32(t_o + c * 32, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st32(t_o + c * 32, o);
+          }
+        } else if (rescale) {
+          l_run *= alpha;  // j == 0 cannot rescale (m_used was -inf); kept for completeness
+        }
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+
+        // pass 2: P = 2^(s * scale - m_used), row sum, 16-bit P for the second MMA
+        float row_sum = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+          float s[32];
+          tmem_ld32(t_s + c * 32, s);
+          unsigned pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2(fmaf(s[i], scale_log2, neg_m));
+            float p1 = ex2(fmaf(s[i + 1], scale_log2, neg_m));
+            if (!full) {
+              const int col = c * 32 + i;
+              if (!(col >= c_lo && col < c_hi)) p0 = 0.f;
+              if (!(col + 1 >= c_lo && col + 1 < c_hi)) p1 = 0.f;
+            }
+            row_sum += p0 + p1;
+            if constexpr (kBf16) {
+              const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+              pk[i / 2] = *reinterpret_cast<const unsigned*>(&hh);
+            } else {
+              const __half2 hh = __floats2half2_rn(p0, p1);
+              pk[i / 2] = *reinterpret_cast<const unsigned*>(&hh);
+            }
+          }
+          if constexpr (kPInTmem) {
+            // keys 32c..32c+31 as 16 packed columns; overwrites S columns already consumed
+            tmem_st16(t_s + c * 16, pk);
+          } else {
+            // K-major 128B-swizzled P tile: row r, 16-byte piece q of the 64-key box at
+            // r * 128 + ((q ^ (r & 7)) * 16)
+            const unsigned box = s_p + w * C::kPBytes + (c / 2) * (kBM * 128) + row * 128;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const int piece = (c & 1) * 4 + q4;
+              const unsigned addr = box + ((piece ^ (row & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                           "r"(pk[4 * q4]), "r"(pk[4 * q4 + 1]), "r"(pk[4 * q4 + 2]),
+                           "r"(pk[4 * q4 + 3])
+                           : "memory");
+            }
+          }
+        }
+        l_run += row_sum;
+        if constexpr (kPInTmem) {
+          tmem_wait_st();
+        } else {
+          tmem_wait_st();  // the O rescale above may have stores in flight
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        tc_fence_before();
+        mbar_arrive(bar_p_full + 8 * w);
+      }
+    }
+
+    // ---------------------------------------------------------------- epilogue ----
+    if (ok && n_tiles > 0) ok = mbar_wait(bar_o_done + 8 * w, 0, abort_flag, a.status, 8, n_tiles);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const size_t grow = (static_cast<size_t>(bh) * a.Sq + static_cast<size_t>(sq) * q_seg_len +
+                           (row_valid ? r_in_seg : 0));
+      float* o_g = a.out + grow * D;
+      const bool have = row_valid && n_tiles > 0 && l_run > 0.f;
+      float m_old = -INFINITY, l_old = 0.f;
+      if (!fresh && row_valid) {
+        m_old = a.m[grow];
+        l_old = a.l[grow];
+      }
+      const float m_new = have ? m_true * kLn2 : -INFINITY;  // natural-log units
+      const float m_fin = fmaxf(m_old, m_new);
+      const float ca = (m_old == -INFINITY) ? 0.f : expf(m_old - m_fin);
+      // O and l are relative to m_used; bring them to m_fin
+      const float cb = have ? ex2(m_used - m_true) * expf(m_new - m_fin) : 0.f;
+      const float l_fin = ca * l_old + cb * l_run;
+      const float inv = finalize ? (l_fin > 0.f ? 1.f / l_fin : 0.f) : 1.f;
+      // a row that saw nothing keeps its state unless the caller asked to overwrite / normalise
+      const bool touch = row_valid && (have || fresh || finalize);
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (n_tiles > 0) {  // block-uniform: the tensor-memory load is warp-collective
+          tmem_ld32(t_o + c * 32, o);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+        if (touch) {
+          float4* dst = reinterpret_cast<float4*>(o_g + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!fresh) old = dst[i];
+            float4 r;
+            r.x = (ca * old.x + (have ? cb * o[4 * i] : 0.f)) * inv;
+            r.y = (ca * old.y + (have ? cb * o[4 * i + 1] : 0.f)) * inv;
+            r.z = (ca * old.z + (have ? cb * o[4 * i + 2] : 0.f)) * inv;
+            r.w = (ca * old.w + (have ? cb * o[4 * i + 3] : 0.f)) * inv;
+            dst[i] = r;
+          }
+        }
+      }
+      if (touch) {
+        a.m[grow] = m_fin;
+        a.l[grow] = l_fin;
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // give copies and MMAs still in flight time to land before tensor memory is released
+      const unsigned long long t0 = global_ns();
+      while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base)
+                 : "memory");
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// (D, rows, heads) 16-bit tensor, box = 64 elements x 128 rows x 1, 128B swizzle.
+int make_map(CUtensorMap* map, int dtype, const void* base, int D, long long rows,
+             long long heads, long long head_stride_elems) {
+  EncodeTiledFn fn = encode_fn();
+  RAB_REQUIRE(fn != nullptr, RA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(heads)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2,
+                                 static_cast<cuuint64_t>(head_stride_elems) * 2};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r =
+      fn(map, dtype == RA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+         3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RAB_REQUIRE(r == CUDA_SUCCESS, RA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d",
+              static_cast<int>(r));
+  return RA_OK;
+}
+
+int g_p_in_tmem = 1;  // which P path the launcher uses (both are kept buildable and tested)
+
+template <int D, bool kBf16, bool kPInTmem>
+int launch_cfg(const StepArgs& a, cudaStream_t stream) {
+  using C = TcCfg<D, kPInTmem>;
+  CUtensorMap mq, mk, mv;
+  const int dtype = kBf16 ? RA_BF16 : RA_F16;
+  int rc = make_map(&mq, dtype, a.q, D, a.Sq, static_cast<long long>(a.B) * a.H,
+                    static_cast<long long>(a.Sq) * D);
+  if (rc != RA_OK) return rc;
+  rc = make_map(&mk, dtype, a.k, D, a.Sk, static_cast<long long>(a.B) * a.kvH, a.kv_head_stride);
+  if (rc != RA_OK) return rc;
+  rc = make_map(&mv, dtype, a.v, D, a.Sk, static_cast<long long>(a.B) * a.kvH, a.kv_head_stride);
+  if (rc != RA_OK) return rc;
+
+  TcArgs t;
+  t.out = a.out;
+  t.m = a.m;
+  t.l = a.l;
+  t.H = a.H;
+  t.kvH = a.kvH;
+  t.Sq = a.Sq;
+  t.n_qblocks_per_seg = (a.qmap.seg_len + kQBlock - 1) / kQBlock;
+  t.qmap = a.qmap;
+  t.kmap = a.kmap;
+  t.stride = a.stride;
+  t.flags = a.flags;
+  t.doc_len = a.doc_len;
+  t.status = a.status;
+  const long long n_qblocks = static_cast<long long>(t.n_qblocks_per_seg) * a.qmap.n_seg;
+  RAB_REQUIRE(n_qblocks <= 65535, RA_ERR_INVALID, "attention step: too many query blocks (%lld)",
+              n_qblocks);
+  auto kern = step_tc_kernel<D, kBf16, kPInTmem>;
+  RAB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+  const dim3 grid(static_cast<unsigned>(a.B) * a.H, static_cast<unsigned>(n_qblocks));
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, t);
+  RAB_CUDA(cudaGetLastError());
+  return RA_OK;
+}
+
+template <int D>
+int launch_d(int dtype, const StepArgs& a, cudaStream_t stream) {
+  if (dtype == RA_BF16) {
+    return g_p_in_tmem ? launch_cfg<D, true, true>(a, stream) : launch_cfg<D, true, false>(a, stream);
+  }
+  return g_p_in_tmem ? launch_cfg<D, false, true>(a, stream) : launch_cfg<D, false, false>(a, stream);
+}
+
+}  // namespace
+
+bool step_tc_supported(int dtype, const StepArgs& a) {
+  if (dtype != RA_F16 && dtype != RA_BF16) return false;
+  if (a.D != 64 && a.D != 128) return false;
+  if (a.Sq <= 0 || a.Sk <= 0) return false;
+  if (a.qmap.n_seg * a.qmap.seg_len != a.Sq || a.kmap.n_seg * a.kmap.seg_len != a.Sk) return false;
+  if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
+       reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.out)) & 15u)
+    return false;
+  return true;
+}
+
+int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream) {
+  RAB_REQUIRE(a.status != nullptr, RA_ERR_CUDA, "attention step: no device status word");
+  if (a.D == 64) return launch_d<64>(dtype, a, stream);
+  return launch_d<128>(dtype, a, stream);
+}
+
+void set_tc_p_in_tmem(int on) { g_p_in_tmem = on ? 1 : 0; }
+
+}  // namespace rab
