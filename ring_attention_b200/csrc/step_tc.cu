@@ -210,9 +210,10 @@ __device__ inline unsigned long long desc_kmajor(unsigned saddr) {
 }
 // MN-major operand (rows = contraction index, 64 contiguous elements of N per 128-byte row):
 // leading byte offset = distance between 64-element N blocks, stride = between 8-row groups.
-__device__ inline unsigned long long desc_mnmajor(unsigned saddr, unsigned lbo_bytes) {
+__device__ inline unsigned long long desc_mnmajor(unsigned saddr, unsigned lbo_bytes,
+                                               unsigned sbo_bytes) {
   const unsigned lo = ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
-  const unsigned hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  const unsigned hi = ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
   return (static_cast<unsigned long long>(hi) << 32) | lo;
 }
 
@@ -277,6 +278,9 @@ struct TcArgs {
   unsigned flags;
   long long doc_len;
   int* status;
+  // shared-memory descriptor parameters of the V operand (bytes); fixed values in normal use,
+  // adjustable through ra_debug_set_tc_knob for bring-up diagnostics
+  unsigned v_lbo, v_sbo, v_kstep;
 };
 
 template <int D, bool kBf16, bool kPInTmem>
@@ -414,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const unsigned vb = s_kv + slot * C::kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks) {
-          const unsigned long long bd = desc_mnmajor(vb + ks * 2048, kBN * 128);
+          const unsigned long long bd = desc_mnmajor(vb + ks * a.v_kstep, a.v_lbo, a.v_sbo);
           const unsigned accum = (acc || ks > 0) ? 1u : 0u;
           if constexpr (kPInTmem) {
             mma_ts(t_o[w], t_s[w] + ks * 8, bd, idesc_pv, accum);
@@ -727,6 +731,9 @@ int make_map(CUtensorMap* map, int dtype, const void* base, int D, long long row
 }
 
 int g_p_in_tmem = 1;  // which P path the launcher uses (both are kept buildable and tested)
+// V operand descriptor: 64-element blocks of the head dimension are one 128-row box
+// (16 KiB) apart, 8-key groups 1 KiB apart, one MMA (16 keys) advances 2 KiB.
+unsigned g_v_lbo = kBN * 128, g_v_sbo = 1024, g_v_kstep = 2048;
 
 template <int D, bool kBf16, bool kPInTmem>
 int launch_cfg(const StepArgs& a, cudaStream_t stream) {
@@ -755,6 +762,9 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.flags = a.flags;
   t.doc_len = a.doc_len;
   t.status = a.status;
+  t.v_lbo = g_v_lbo;
+  t.v_sbo = g_v_sbo;
+  t.v_kstep = g_v_kstep;
   const long long n_qblocks = static_cast<long long>(t.n_qblocks_per_seg) * a.qmap.n_seg;
   RAB_REQUIRE(n_qblocks <= 65535, RA_ERR_INVALID, "attention step: too many query blocks (%lld)",
               n_qblocks);
@@ -794,5 +804,11 @@ int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream) {
 }
 
 void set_tc_p_in_tmem(int on) { g_p_in_tmem = on ? 1 : 0; }
+
+void set_tc_knob(int which, unsigned value) {
+  if (which == 1) g_v_lbo = value;
+  if (which == 2) g_v_sbo = value;
+  if (which == 3) g_v_kstep = value;
+}
 
 }  // namespace rab
