@@ -251,8 +251,8 @@ int ra_attention_lse(const float* m, const float* l, float* lse, size_t count, r
 }
 
 int ra_float_to_half(const float* src, void* dst, size_t n, ra_stream stream) {
-  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_float_to_half: null argument");
   if (n == 0) return RA_OK;
+  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_float_to_half: null argument");
   const int vec = aligned16(src) && aligned16(dst);
   narrow_kernel<__half><<<grid_for(n / 8 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       src, static_cast<__half*>(dst), n, vec);
@@ -261,8 +261,8 @@ int ra_float_to_half(const float* src, void* dst, size_t n, ra_stream stream) {
 }
 
 int ra_float_to_bf16(const float* src, void* dst, size_t n, ra_stream stream) {
-  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_float_to_bf16: null argument");
   if (n == 0) return RA_OK;
+  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_float_to_bf16: null argument");
   const int vec = aligned16(src) && aligned16(dst);
   narrow_kernel<__nv_bfloat16>
       <<<grid_for(n / 8 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -272,8 +272,8 @@ int ra_float_to_bf16(const float* src, void* dst, size_t n, ra_stream stream) {
 }
 
 int ra_half_to_float(const void* src, float* dst, size_t n, ra_stream stream) {
-  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_half_to_float: null argument");
   if (n == 0) return RA_OK;
+  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_half_to_float: null argument");
   const int vec = aligned16(src) && aligned16(dst);
   widen_kernel<<<grid_for(n / 8 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half*>(src), dst, n, vec);
@@ -282,16 +282,16 @@ int ra_half_to_float(const void* src, float* dst, size_t n, ra_stream stream) {
 }
 
 int ra_float_to_int8(const float* src, signed char* dst, size_t n, ra_stream stream) {
-  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_float_to_int8: null argument");
   if (n == 0) return RA_OK;
+  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_float_to_int8: null argument");
   to_int8_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(src, dst, n);
   RAB_CUDA(cudaGetLastError());
   return RA_OK;
 }
 
 int ra_int8_to_float(const signed char* src, float* dst, size_t n, ra_stream stream) {
-  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_int8_to_float: null argument");
   if (n == 0) return RA_OK;
+  RAB_REQUIRE(src && dst, RA_ERR_INVALID, "ra_int8_to_float: null argument");
   from_int8_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(src, dst, n);
   RAB_CUDA(cudaGetLastError());
   return RA_OK;
