@@ -361,8 +361,54 @@ def bench_decode(api, torch, dev, args, peaks):
             "gpu_launches_per_step": 4}
 
 
+def run_profile_case(args):
+    """A small, self-ending case for `ncu`: few launches, at most ~1 GB on the device.
+    prefill: the benchmark's own shape (100 MB of Q/K/V, larger than L2 together with the 67 MB
+    output), 1 warm-up + 2 launches of the step kernel. decode: the decode workload at a
+    quarter of the cached length (65536 tokens, 1 GB of K/V), 1 warm-up + 2 steps."""
+    import torch
+
+    from ring_attention_b200 import api
+    from ring_attention_b200._lib import SegMap
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(42)
+    if args.profile == "prefill":
+        w = WORKLOAD
+        B, H, S, D = w["batch"], w["heads"], w["seq"], w["head_dim"]
+        q, k, v = (torch.randn((B, H, S, D), generator=g, device=dev, dtype=torch.float16) for _ in range(3))
+        out = torch.empty((B, H, S, D), device=dev)
+        m = torch.empty((B, H, S), device=dev)
+        l = torch.empty_like(m)
+        part = api.RingPartition(1, 0, S, api.RingPartition.ZIGZAG, w["n_splits"])
+        qmap, kmap, stride = part.step_maps(0)
+        for _ in range(3):
+            api.attention_step_ex(q, k, v, out, m, l, api.AttentionShape(B, H, S, S, D), qmap, kmap, stride,
+                                  causal=True, fresh=True, finalize=True)
+    else:
+        d = DECODE
+        B, H, kvH, D, L = d["batch"], d["heads"], d["kv_heads"], d["head_dim"], d["prompt"] // 4
+        k = torch.randn((B, kvH, L, D), generator=g, device=dev, dtype=torch.float16)
+        v = torch.randn((B, kvH, L, D), generator=g, device=dev, dtype=torch.float16)
+        q = torch.randn((B, H, 1, D), generator=g, device=dev, dtype=torch.float16)
+        shape = api.AttentionShape(B, H, 1, L, D, kvH)
+        out = torch.empty((B, H, 1, D), device=dev)
+        m = torch.empty((B, H, 1), device=dev)
+        l = torch.empty_like(m)
+        for _ in range(3):
+            api.launch_attention_init(out, m, l, shape)
+            api.launch_attention_decode_step(q, k, v, out, m, l, shape, 0, 0, False)
+            api.launch_attention_finalize(out, l, shape)
+    torch.cuda.synchronize()
+    assert api.device_status()[0] == 0
+    print(json.dumps({"profile_case": args.profile, "ok": True}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode"],
+                    help="run a small self-ending case for ncu instead of the benchmark")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -370,6 +416,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
+    if args.profile:
+        return run_profile_case(args)
     if args.impl == "reference":
         return run_reference_arm(args)
     return run_gpu_arm(args)
