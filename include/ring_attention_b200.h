@@ -178,6 +178,24 @@ RA_API int ra_attention_decode_step(int dtype, const void* q, const void* k, con
                                     int q_offset, int k_offset, int causal, ra_stream stream,
                                     int kv_row_stride, void* workspace, size_t workspace_bytes);
 
+/* The same decode step for callers that cannot allocate device memory: processes that gave
+ * all of it to their own arena, callers inside a section where the CUDA allocator must not
+ * be entered, embedders that forbid hidden allocations. It has no counterpart in the
+ * reference. The split partials go to a 1 MiB array built into the library image (each GPU
+ * that loads the library holds it until exit); the call makes no cudaMalloc / cudaFree or
+ * any other allocating call. Limit: batch * heads * (head_dim + 2) floats must fit the array
+ * (262144 floats); larger problems are refused with RA_ERR_OVERFLOW and a message naming the
+ * limit, and fewer splits are used when the usual split count would not fit. The first call
+ * on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current), so make that first call outside any stream capture. All calls on a device share
+ * the one array: two calls whose kernels may overlap on the GPU (different streams) race;
+ * serialise them. The array keeps the previous call's contents, which is harmless because
+ * each call writes every slot before reading it. Arguments as ra_attention_decode_step. */
+RA_API int ra_attention_decode_step_noalloc(int dtype, const void* q, const void* k,
+                                            const void* v, float* out, float* m, float* l,
+                                            const ra_shape* shape, int q_offset, int k_offset,
+                                            int causal, ra_stream stream, int kv_row_stride);
+
 /* Merge cp_size rank partials laid out as cp_size blocks [O (BH*D) | m (BH) | l (BH)]
  * into (out, m_out, l_out); with normalise != 0 also divides out by l. Replaces
  * decode_partial_merge_kernel (+ the finalize after it) (src/ring_decode.cu:50-81,192-203). */

@@ -92,6 +92,8 @@ _SIG = {
     "ra_attention_decode_step": (C.c_int, [C.c_int, _P, _P, _P, _P, _P, _P, C.POINTER(Shape),
                                            C.c_int, C.c_int, C.c_int, _P, C.c_int, _P,
                                            C.c_size_t]),
+    "ra_attention_decode_step_noalloc": (C.c_int, [C.c_int, _P, _P, _P, _P, _P, _P, C.POINTER(Shape),
+                                                   C.c_int, C.c_int, C.c_int, _P, C.c_int]),
     "ra_decode_partial_merge": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "ra_kv_cache_create": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                      C.POINTER(_P)]),

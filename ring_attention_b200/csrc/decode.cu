@@ -358,7 +358,8 @@ int sm_count() {
   return v > 0 ? v : 148;
 }
 
-Plan make_plan(int B, int H, int kvH, int sk_eff, int rows_per_stage, int sms) {
+Plan make_plan(int B, int H, int kvH, int sk_eff, int rows_per_stage, int sms,
+               int split_cap = kMaxSplits) {
   Plan p;
   const int group = (H + kvH - 1) / kvH;  // query heads per KV head (largest group)
   p.gb = group > 4 ? 8 : (group > 2 ? 4 : (group > 1 ? 2 : 1));  // smallest of 1/2/4/8 that fits
@@ -366,7 +367,7 @@ Plan make_plan(int B, int H, int kvH, int sk_eff, int rows_per_stage, int sms) {
   const int blocks_per_split = B * kvH * p.head_batches;
   int want = (3 * sms + blocks_per_split - 1) / blocks_per_split;
   const int max_by_rows = std::max(1, sk_eff / (2 * rows_per_stage));
-  want = std::max(1, std::min(std::min(want, max_by_rows), kMaxSplits));
+  want = std::max(1, std::min(std::min(want, max_by_rows), split_cap));
   int rps = (sk_eff + want - 1) / want;
   rps = ((rps + rows_per_stage - 1) / rows_per_stage) * rows_per_stage;
   if (rps < rows_per_stage) rps = rows_per_stage;
@@ -404,10 +405,12 @@ int ensure_workspace(size_t need, void** out) {
 template <typename T, int D>
 int launch_decode_typed(const void* q, const void* k, const void* v, float* out, float* m,
                         float* l, const ra_shape& s, int sk_eff, long long kv_head_stride,
-                        void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                        void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                        int split_cap = kMaxSplits) {
   using C = DecodeCfg<T, D>;
   const int kvH = kv_heads_of(s);
-  const Plan p = make_plan(s.batch, s.heads, kvH, sk_eff, C::kRowsPerStage, sm_count());
+  const Plan p =
+      make_plan(s.batch, s.heads, kvH, sk_eff, C::kRowsPerStage, sm_count(), split_cap);
   const size_t prow = static_cast<size_t>(p.n_split) * s.batch * s.heads;
   const size_t need = prow * (D + 2) * sizeof(float);
   if (workspace == nullptr) {
@@ -451,20 +454,21 @@ int launch_decode_typed(const void* q, const void* k, const void* v, float* out,
 template <typename T>
 int launch_decode_dtype(const void* q, const void* k, const void* v, float* out, float* m,
                         float* l, const ra_shape& s, int sk_eff, long long kv_head_stride,
-                        void* ws, size_t ws_bytes, cudaStream_t stream) {
+                        void* ws, size_t ws_bytes, cudaStream_t stream,
+                        int split_cap = kMaxSplits) {
   switch (s.head_dim) {
     case 32:
       return launch_decode_typed<T, 32>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                        ws_bytes, stream);
+                                        ws_bytes, stream, split_cap);
     case 64:
       return launch_decode_typed<T, 64>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                        ws_bytes, stream);
+                                        ws_bytes, stream, split_cap);
     case 128:
       return launch_decode_typed<T, 128>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                         ws_bytes, stream);
+                                         ws_bytes, stream, split_cap);
     case 256:
       return launch_decode_typed<T, 256>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                         ws_bytes, stream);
+                                         ws_bytes, stream, split_cap);
   }
   set_error("attention_decode_step: unsupported head_dim=%d (supported: 32, 64, 128, 256)",
             s.head_dim);
@@ -507,9 +511,102 @@ int decode_step(int dtype, const void* q, const void* k, const void* v, float* o
   return RA_ERR_INVALID;
 }
 
+// ---- decode step that never allocates --------------------------------------------------
+//
+// Some hosts of this library may not call cudaMalloc at all: a serving process that handed
+// its whole memory budget to one arena at start-up, a caller inside a region where the
+// allocator is locked (a stream being captured, a real-time loop that must not take the
+// driver's allocation lock), or an embedder whose policy forbids a library to allocate behind
+// its back. For them the split partials live in a fixed array that is part of the library
+// image: every GPU that loads the library holds these kStaticScratchFloats * 4 bytes (1 MiB)
+// until the process exits.
+constexpr size_t kStaticScratchFloats = 262144;  // 1 MiB
+static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchFloats];
+
+// Device address of the array on the CURRENT device. In host code the array's name is only a
+// host-side handle for the symbol, never a device pointer, so the address is asked for once
+// per device (with that device current) and cached.
+int static_scratch_ptr(float** out) {
+  static float* cache[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  RAB_CUDA(cudaGetDevice(&dev));
+  RAB_REQUIRE(dev >= 0 && dev < 64, RA_ERR_INVALID, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (cache[dev] == nullptr) {
+    void* p = nullptr;
+    RAB_CUDA(cudaGetSymbolAddress(&p, g_decode_static_scratch));
+    RAB_REQUIRE(p != nullptr, RA_ERR_CUDA, "no device address for the static decode scratch");
+    cache[dev] = static_cast<float*>(p);
+  }
+  *out = cache[dev];
+  return RA_OK;
+}
+
+int decode_step_noalloc(int dtype, const void* q, const void* k, const void* v, float* out,
+                        float* m, float* l, const ra_shape& s, int q_offset, int k_offset,
+                        int causal, cudaStream_t stream, int kv_row_stride) {
+  RAB_REQUIRE(q && k && v && out && m && l, RA_ERR_INVALID, "decode step: null argument");
+  RAB_REQUIRE(s.seq_q == 1, RA_ERR_INVALID, "decode step: seq_q must be 1 (got %d)", s.seq_q);
+  RAB_REQUIRE(s.batch > 0 && s.heads > 0 && s.batch <= 65535, RA_ERR_INVALID,
+              "decode step: bad batch/heads");
+  RAB_REQUIRE(s.head_dim == 32 || s.head_dim == 64 || s.head_dim == 128 || s.head_dim == 256,
+              RA_ERR_UNSUPPORTED,
+              "attention_decode_step: unsupported head_dim=%d (supported: 32, 64, 128, 256)",
+              s.head_dim);
+  RAB_REQUIRE((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+               reinterpret_cast<uintptr_t>(v)) % 16 == 0,
+              RA_ERR_INVALID, "decode step: q, k and v must be 16-byte aligned");
+  // One split needs batch * heads * (head_dim + 2) floats; the array must hold at least one.
+  const size_t per_split = static_cast<size_t>(s.batch) * s.heads * (s.head_dim + 2);
+  RAB_REQUIRE(per_split <= kStaticScratchFloats, RA_ERR_OVERFLOW,
+              "ra_attention_decode_step_noalloc: batch*heads*(head_dim+2) = %zu floats exceeds the "
+              "built-in scratch of %zu floats (1 MiB); use ra_attention_decode_step with a "
+              "caller-provided workspace",
+              per_split, kStaticScratchFloats);
+  const int split_cap =
+      static_cast<int>(std::min<size_t>(kMaxSplits, kStaticScratchFloats / per_split));
+  float* scratch = nullptr;
+  const int rc = static_scratch_ptr(&scratch);
+  if (rc != RA_OK) return rc;
+  int sk_eff = s.seq_k;
+  if (causal) {
+    const long long vis = static_cast<long long>(q_offset) - k_offset + 1;
+    if (vis < sk_eff) sk_eff = vis < 0 ? 0 : static_cast<int>(vis);
+  }
+  if (sk_eff <= 0) return RA_OK;
+  const int stride_rows = kv_row_stride > 0 ? kv_row_stride : s.seq_k;
+  const long long kv_head_stride = static_cast<long long>(stride_rows) * s.head_dim;
+  const size_t bytes = kStaticScratchFloats * sizeof(float);
+  // Nothing in the array has to start at zero: every (split, batch, head) slot the reduce
+  // kernel reads is written by the split kernel of the same call first.
+  switch (dtype) {
+    case RA_F32:
+      return launch_decode_dtype<float>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, scratch,
+                                        bytes, stream, split_cap);
+    case RA_F16:
+      return launch_decode_dtype<__half>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, scratch,
+                                         bytes, stream, split_cap);
+    case RA_BF16:
+      return launch_decode_dtype<__nv_bfloat16>(q, k, v, out, m, l, s, sk_eff, kv_head_stride,
+                                                scratch, bytes, stream, split_cap);
+  }
+  set_error("decode step: unknown dtype %d", dtype);
+  return RA_ERR_INVALID;
+}
+
 }  // namespace rab
 
 extern "C" {
+
+int ra_attention_decode_step_noalloc(int dtype, const void* q, const void* k, const void* v,
+                                     float* out, float* m, float* l, const ra_shape* shape,
+                                     int q_offset, int k_offset, int causal, ra_stream stream,
+                                     int kv_row_stride) {
+  RAB_REQUIRE(shape != nullptr, RA_ERR_INVALID, "ra_attention_decode_step_noalloc: null shape");
+  return rab::decode_step_noalloc(dtype, q, k, v, out, m, l, *shape, q_offset, k_offset, causal,
+                                  static_cast<cudaStream_t>(stream), kv_row_stride);
+}
 
 size_t ra_decode_workspace_bytes(const ra_shape* shape) {
   if (!shape) return 0;
