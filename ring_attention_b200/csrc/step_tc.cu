@@ -164,6 +164,37 @@ __device__ inline void tmem_ld32(unsigned taddr, float (&r)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
 }
+// All 128 columns of a row: four 32-column loads in flight and one wait, in a single asm
+// statement so that no use of the registers can be scheduled above the wait.
+__device__ inline void tmem_ld128(unsigned taddr, float (&r)[128]) {
+  unsigned u[128];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%128];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%129];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%64, %65, %66, %67, %68, %69, %70, %71, %72, %73, %74, %75, %76, %77, %78, %79, %80, %81, %82, %83, %84, %85, %86, %87, %88, %89, %90, %91, %92, %93, %94, %95}, [%130];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%96, %97, %98, %99, %100, %101, %102, %103, %104, %105, %106, %107, %108, %109, %110, %111, %112, %113, %114, %115, %116, %117, %118, %119, %120, %121, %122, %123, %124, %125, %126, %127}, [%131];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+        "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
+        "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
+        "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31]),
+        "=r"(u[32]), "=r"(u[33]), "=r"(u[34]), "=r"(u[35]), "=r"(u[36]), "=r"(u[37]), "=r"(u[38]), "=r"(u[39]),
+        "=r"(u[40]), "=r"(u[41]), "=r"(u[42]), "=r"(u[43]), "=r"(u[44]), "=r"(u[45]), "=r"(u[46]), "=r"(u[47]),
+        "=r"(u[48]), "=r"(u[49]), "=r"(u[50]), "=r"(u[51]), "=r"(u[52]), "=r"(u[53]), "=r"(u[54]), "=r"(u[55]),
+        "=r"(u[56]), "=r"(u[57]), "=r"(u[58]), "=r"(u[59]), "=r"(u[60]), "=r"(u[61]), "=r"(u[62]), "=r"(u[63]),
+        "=r"(u[64]), "=r"(u[65]), "=r"(u[66]), "=r"(u[67]), "=r"(u[68]), "=r"(u[69]), "=r"(u[70]), "=r"(u[71]),
+        "=r"(u[72]), "=r"(u[73]), "=r"(u[74]), "=r"(u[75]), "=r"(u[76]), "=r"(u[77]), "=r"(u[78]), "=r"(u[79]),
+        "=r"(u[80]), "=r"(u[81]), "=r"(u[82]), "=r"(u[83]), "=r"(u[84]), "=r"(u[85]), "=r"(u[86]), "=r"(u[87]),
+        "=r"(u[88]), "=r"(u[89]), "=r"(u[90]), "=r"(u[91]), "=r"(u[92]), "=r"(u[93]), "=r"(u[94]), "=r"(u[95]),
+        "=r"(u[96]), "=r"(u[97]), "=r"(u[98]), "=r"(u[99]), "=r"(u[100]), "=r"(u[101]), "=r"(u[102]), "=r"(u[103]),
+        "=r"(u[104]), "=r"(u[105]), "=r"(u[106]), "=r"(u[107]), "=r"(u[108]), "=r"(u[109]), "=r"(u[110]), "=r"(u[111]),
+        "=r"(u[112]), "=r"(u[113]), "=r"(u[114]), "=r"(u[115]), "=r"(u[116]), "=r"(u[117]), "=r"(u[118]), "=r"(u[119]),
+        "=r"(u[120]), "=r"(u[121]), "=r"(u[122]), "=r"(u[123]), "=r"(u[124]), "=r"(u[125]), "=r"(u[126]), "=r"(u[127])
+      : "r"(taddr), "r"(taddr + 32), "r"(taddr + 64), "r"(taddr + 96)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 128; ++i) r[i] = __uint_as_float(u[i]);
+}
 __device__ inline void tmem_st32(unsigned taddr, const float (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -190,6 +221,53 @@ __device__ inline void tmem_st16(unsigned taddr, const unsigned (&u)[16]) {
       "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
       "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15])
       : "memory");
+}
+// 32 packed columns from an array slice
+__device__ inline void tmem_st32u(unsigned taddr, const unsigned* u) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
+          taddr),
+      "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+      "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]),
+      "r"(u[15]), "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]),
+      "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]),
+      "r"(u[29]), "r"(u[30]), "r"(u[31])
+      : "memory");
+}
+__device__ inline float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// packed fp32x2 arithmetic: one instruction for two lanes of a float2
+__device__ inline float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)),
+        "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return d;
+}
+__device__ inline float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)),
+        "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return d;
+}
+template <bool kBf16>
+__device__ inline unsigned pack16(float lo, float hi) {
+  if constexpr (kBf16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&h);
+  } else {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&h);
+  }
 }
 __device__ inline void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -366,6 +444,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
 
+  // Registers follow the work: the producer / MMA warpgroup gives most of its registers back,
+  // the two softmax warpgroups (one row of 128 scores per thread) take them.
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ----
     if (lane == 0 && n_tiles > 0) {
@@ -466,7 +548,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ----------------------------------------------------------------- softmax ----
     const int w = (warp - 4) >> 2;                   // query tile of this warpgroup
     const int row = ((warp & 3) << 5) + lane;        // row inside the tile = TMEM lane
@@ -517,21 +601,19 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) break;
         tc_fence_after();
 
-        // pass 1: row maximum over the visible columns
+        // All 128 scores of the row in registers: four loads in flight, one wait.
+        float s[kBN];
+        tmem_ld128(t_s, s);
         float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
-          float s[32];
-          tmem_ld32(t_s + c * 32, s);
-          if (full) {
+        if (full) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
-          } else {
+          for (int i = 0; i < kBN; i += 2) mx = max3(mx, s[i], s[i + 1]);
+        } else {
+          // hidden columns become -inf, which the exponential below turns into exactly 0
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int col = c * 32 + i;
-              if (col >= c_lo && col < c_hi) mx = fmaxf(mx, s[i]);
-            }
+          for (int i = 0; i < kBN; ++i) {
+            s[i] = (i >= c_lo && i < c_hi) ? s[i] : -INFINITY;
+            mx = fmaxf(mx, s[i]);
           }
         }
         const float tile_max = mx * scale_log2;  // -inf stays -inf (scale > 0)
@@ -559,52 +641,42 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int i = 0; i < 32; ++i) o[i] *= alpha;
             tmem_st32(t_o + c * 32, o);
           }
-        } else if (rescale) {
-          l_run *= alpha;  // j == 0 cannot rescale (m_used was -inf); kept for completeness
         }
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
 
-        // pass 2: P = 2^(s * scale - m_used), row sum, 16-bit P for the second MMA
-        float row_sum = 0.f;
-#pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
-          float s[32];
-          tmem_ld32(t_s + c * 32, s);
-          unsigned pk[16];
+        // P = 2^(s * scale - m_used) two columns at a time (packed fp32x2 multiply-add and
+        // add), row sum in two independent accumulators, 16-bit P for the second MMA.
+        const float2 scale2 = make_float2(scale_log2, scale_log2);
+        const float2 negm2 = make_float2(neg_m, neg_m);
+        float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+        unsigned pk[kBN / 2];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = ex2(fmaf(s[i], scale_log2, neg_m));
-            float p1 = ex2(fmaf(s[i + 1], scale_log2, neg_m));
-            if (!full) {
-              const int col = c * 32 + i;
-              if (!(col >= c_lo && col < c_hi)) p0 = 0.f;
-              if (!(col + 1 >= c_lo && col + 1 < c_hi)) p1 = 0.f;
-            }
-            row_sum += p0 + p1;
-            if constexpr (kBf16) {
-              const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-              pk[i / 2] = *reinterpret_cast<const unsigned*>(&hh);
-            } else {
-              const __half2 hh = __floats2half2_rn(p0, p1);
-              pk[i / 2] = *reinterpret_cast<const unsigned*>(&hh);
-            }
-          }
-          if constexpr (kPInTmem) {
-            // keys 32c..32c+31 as 16 packed columns; overwrites S columns already consumed
-            tmem_st16(t_s + c * 16, pk);
-          } else {
-            // K-major 128B-swizzled P tile: row r, 16-byte piece q of the 64-key box at
-            // r * 128 + ((q ^ (r & 7)) * 16)
-            const unsigned box = s_p + w * C::kPBytes + (c / 2) * (kBM * 128) + row * 128;
+        for (int i = 0; i < kBN; i += 4) {
+          const float2 x0 = ffma2(make_float2(s[i], s[i + 1]), scale2, negm2);
+          const float2 x1 = ffma2(make_float2(s[i + 2], s[i + 3]), scale2, negm2);
+          const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
+          const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
+          sum_a = fadd2(sum_a, p0);
+          sum_b = fadd2(sum_b, p1);
+          pk[i / 2] = pack16<kBf16>(p0.x, p0.y);
+          pk[i / 2 + 1] = pack16<kBf16>(p1.x, p1.y);
+        }
+        const float row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        if constexpr (kPInTmem) {
+          // keys 0..127 as 64 packed columns over the S columns, which are all consumed by now
+          tmem_st32u(t_s, &pk[0]);
+          tmem_st32u(t_s + 32, &pk[32]);
+        } else {
+          // K-major 128B-swizzled P tile: row r, 16-byte piece q of a 64-key box at
+          // r * 128 + ((q ^ (r & 7)) * 16)
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              const int piece = (c & 1) * 4 + q4;
-              const unsigned addr = box + ((piece ^ (row & 7)) << 4);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
-                           "r"(pk[4 * q4]), "r"(pk[4 * q4 + 1]), "r"(pk[4 * q4 + 2]),
-                           "r"(pk[4 * q4 + 3])
-                           : "memory");
-            }
+          for (int piece = 0; piece < 16; ++piece) {
+            const unsigned box = s_p + w * C::kPBytes + (piece / 8) * (kBM * 128) + row * 128;
+            const unsigned addr = box + (((piece & 7) ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                         "r"(pk[4 * piece]), "r"(pk[4 * piece + 1]), "r"(pk[4 * piece + 2]),
+                         "r"(pk[4 * piece + 3])
+                         : "memory");
           }
         }
         l_run += row_sum;
