@@ -10,7 +10,6 @@
 namespace rab {
 
 void set_tc_p_in_tmem(int on);
-void set_tc_knob(int which, unsigned value);
 
 namespace {
 
@@ -130,9 +129,7 @@ int ra_attention_step_ex(int dtype, const void* q, const void* k, const void* v,
 
 // Test hook: 1 = keep P in tensor memory (default), 0 = stage P through shared memory.
 RA_API void ra_debug_set_p_in_tmem(int on) { rab::set_tc_p_in_tmem(on); }
-// Bring-up hook: V-operand descriptor fields in bytes (1 = leading offset, 2 = stride offset,
-// 3 = advance per 16-key MMA). Not part of the supported interface.
-RA_API void ra_debug_set_tc_knob(int which, unsigned value) { rab::set_tc_knob(which, value); }
+
 
 /* ------------------------------------------------ whole attention, device buffers ---- */
 

@@ -51,6 +51,20 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O when the max moved > 2^8
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
 
+#ifdef RAB_TRACE
+// Bring-up timeline (compiled only with -DRAB_TRACE): clock64 stamps of block (0,0) for the
+// first 64 tiles; roles 0/1 = first lane of the two softmax groups, 2 = the MMA lane.
+__device__ long long g_trace[3][64][8];
+#define RAB_TR(role, tile, k)                                                  \
+  do {                                                                         \
+    if (trace_on && (tile) < 64) g_trace[role][tile][k] = clock64();          \
+  } while (0)
+#else
+#define RAB_TR(role, tile, k) \
+  do {                        \
+  } while (0)
+#endif
+
 // ---- PTX wrappers -------------------------------------------------------------------
 __device__ inline unsigned smem_u32(const void* p) {
   return static_cast<unsigned>(__cvta_generic_to_shared(p));
@@ -287,7 +301,8 @@ __device__ inline unsigned long long desc_kmajor(unsigned saddr) {
   return (static_cast<unsigned long long>(hi) << 32) | lo;
 }
 // MN-major operand (rows = contraction index, 64 contiguous elements of N per 128-byte row):
-// leading byte offset = distance between 64-element N blocks, stride = between 8-row groups.
+// leading byte offset = distance between 64-element N blocks (one 128-row box, 16 KiB),
+// stride = between 8-row groups (1 KiB); one MMA (16 rows) advances the start by 2 KiB.
 __device__ inline unsigned long long desc_mnmajor(unsigned saddr, unsigned lbo_bytes,
                                                unsigned sbo_bytes) {
   const unsigned lo = ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
@@ -356,9 +371,6 @@ struct TcArgs {
   unsigned flags;
   long long doc_len;
   int* status;
-  // shared-memory descriptor parameters of the V operand (bytes); fixed values in normal use,
-  // adjustable through ra_debug_set_tc_knob for bring-up diagnostics
-  unsigned v_lbo, v_sbo, v_kstep;
 };
 
 template <int D, bool kBf16, bool kPInTmem>
@@ -389,6 +401,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+#ifdef RAB_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
+#endif
 
   // An earlier block gave up: leave at once (the vote makes the decision block-uniform).
   if (__syncthreads_or(*reinterpret_cast<volatile int*>(a.status) != 0)) return;
@@ -487,26 +502,36 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr unsigned idesc_pv = make_idesc(kFmt, 1, D, kBM);
       const unsigned t_s[2] = {tmem_base + C::kColS0, tmem_base + C::kColS1};
       const unsigned t_o[2] = {tmem_base + C::kColO0, tmem_base + C::kColO1};
+      // Descriptors are built once; inside the issue loops a descriptor is a base plus a
+      // compile-time constant in its 16-byte-unit address field, so the single issuing lane
+      // spends a couple of instructions per MMA.
+      const unsigned long long dq[2] = {desc_kmajor(s_q), desc_kmajor(s_q + C::kTileBytes)};
+      const unsigned long long dkv0_k = desc_kmajor(s_kv);
+      const unsigned long long dkv0_v = desc_mnmajor(s_kv, kBN * 128, 1024);
+      [[maybe_unused]] const unsigned long long dp[2] = {desc_kmajor(s_p),
+                                                         desc_kmajor(s_p + C::kPBytes)};
+      constexpr unsigned kSlotUnits = C::kTileBytes >> 4;  // one ring slot in 16-byte units
       auto issue_s = [&](int w, int slot) {
-        const unsigned qa = s_q + w * C::kTileBytes;
-        const unsigned kb = s_kv + slot * C::kTileBytes;
+        const unsigned long long qd = dq[w];
+        const unsigned long long kd = dkv0_k + static_cast<unsigned long long>(slot * kSlotUnits);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const unsigned off = (ks / 4) * (kBM * 128) + (ks % 4) * 32;
-          mma_ss(t_s[w], desc_kmajor(qa + off), desc_kmajor(kb + off), idesc_s, ks > 0 ? 1u : 0u);
+          constexpr unsigned kBox = (kBM * 128) >> 4;
+          const unsigned off = (ks / 4) * kBox + (ks % 4) * 2;  // 64-element box, 32 B per step
+          mma_ss(t_s[w], qd + off, kd + off, idesc_s, ks > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int w, int slot, bool acc) {
-        const unsigned vb = s_kv + slot * C::kTileBytes;
+        const unsigned long long vd = dkv0_v + static_cast<unsigned long long>(slot * kSlotUnits);
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks) {
-          const unsigned long long bd = desc_mnmajor(vb + ks * a.v_kstep, a.v_lbo, a.v_sbo);
+          const unsigned long long bd = vd + ks * (2048 >> 4);  // 16 keys = two 8-row groups
           const unsigned accum = (acc || ks > 0) ? 1u : 0u;
           if constexpr (kPInTmem) {
             mma_ts(t_o[w], t_s[w] + ks * 8, bd, idesc_pv, accum);
           } else {
-            const unsigned pa = s_p + w * C::kPBytes + (ks / 4) * (kBM * 128) + (ks % 4) * 32;
-            mma_ss(t_o[w], desc_kmajor(pa), bd, idesc_pv, accum);
+            constexpr unsigned kBox = (kBM * 128) >> 4;
+            mma_ss(t_o[w], dp[w] + ((ks / 4) * kBox + (ks % 4) * 2), bd, idesc_pv, accum);
           }
         }
       };
@@ -531,7 +556,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           ok = mbar_wait(bar_kv_full + 8 * slot_k, (it_k / C::kStages) & 1, abort_flag, a.status,
                          5, j);
         for (int w = 0; w < 2 && ok; ++w) {
+          RAB_TR(2, j, 3 * w);
           ok = mbar_wait(bar_p_full + 8 * w, j & 1, abort_flag, a.status, 6, j);
+          RAB_TR(2, j, 3 * w + 1);
           if (!ok) break;
           tc_fence_after();
           issue_pv(w, slot_v, j > 0);
@@ -541,6 +568,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           } else {
             tc_commit(bar_o_done + 8 * w);
           }
+          RAB_TR(2, j, 3 * w + 2);
         }
         if (ok) {
           tc_commit(bar_kv_empty + 8 * slot_v);
@@ -571,32 +599,38 @@ __global__ void __launch_bounds__(kThreads, 1)
     int j = 0;
     for (int sk = 0; sk < a.kmap.n_seg && ok; ++sk) {
       const TileRange tr = tile_range(a.kmap, sk, a.stride, causal, a.doc_len, qmin, qmax);
-      const int k_seg_len = a.kmap.seg_len;
-      for (int t = tr.lo; t < tr.hi && ok; ++t, ++j) {
-        // Visible columns of this row in this tile form an interval [c_lo, c_hi).
-        const long long kpos0 = static_cast<long long>(a.kmap.base[sk]) +
-                                static_cast<long long>(t) * kBN * a.stride;
-        int c_lo = 0, c_hi = min(kBN, k_seg_len - t * kBN);
+      // Keys of this segment the row can see are the local indices [rel_lo, rel_hi): causal
+      // and document limits are affine in the key index, so they are worked out once per
+      // segment (64-bit divisions) and the per-tile work is two 32-bit clamps.
+      int rel_lo = 0, rel_hi = row_valid ? a.kmap.seg_len : 0;
+      {
+        const long long kb = a.kmap.base[sk];
         if (causal) {
-          const long long d = static_cast<long long>(qpos) - kpos0;
-          c_hi = d < 0 ? 0 : static_cast<int>(min(static_cast<long long>(c_hi), d / a.stride + 1));
+          const long long d = static_cast<long long>(qpos) - kb;
+          rel_hi = d < 0 ? 0 : static_cast<int>(min(static_cast<long long>(rel_hi), d / a.stride + 1));
         }
         if (a.doc_len > 0) {
           const long long p_lo = qdoc * a.doc_len, p_hi = p_lo + a.doc_len - 1;
-          if (p_hi < kpos0) {
-            c_hi = 0;
+          if (p_hi < kb) {
+            rel_hi = 0;
           } else {
-            c_hi = static_cast<int>(min(static_cast<long long>(c_hi), (p_hi - kpos0) / a.stride + 1));
-            if (p_lo > kpos0)
-              c_lo = static_cast<int>(min(static_cast<long long>(kBN),
-                                          (p_lo - kpos0 + a.stride - 1) / a.stride));
+            rel_hi = static_cast<int>(min(static_cast<long long>(rel_hi), (p_hi - kb) / a.stride + 1));
+            if (p_lo > kb)
+              rel_lo = static_cast<int>(min(static_cast<long long>(a.kmap.seg_len),
+                                            (p_lo - kb + a.stride - 1) / a.stride));
           }
         }
-        if (!row_valid) c_hi = 0;
+      }
+      for (int t = tr.lo; t < tr.hi && ok; ++t, ++j) {
+        // Visible columns of this row in this tile: [c_lo, c_hi), from the segment's bounds.
+        int c_lo = min(max(rel_lo - t * kBN, 0), kBN);
+        int c_hi = min(max(rel_hi - t * kBN, 0), kBN);
         if (c_hi < c_lo) c_hi = c_lo;
         const bool full = __all_sync(0xffffffffu, c_lo == 0 && c_hi == kBN);
 
+        RAB_TR(w, j, 0);
         ok = mbar_wait(bar_s_full + 8 * w, j & 1, abort_flag, a.status, 7, j);
+        RAB_TR(w, j, 1);
         ok = __all_sync(0xffffffffu, ok);  // the tensor-memory accesses below are warp-collective
         if (!ok) break;
         tc_fence_after();
@@ -604,10 +638,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         // All 128 scores of the row in registers: four loads in flight, one wait.
         float s[kBN];
         tmem_ld128(t_s, s);
+        RAB_TR(w, j, 2);
         float mx = -INFINITY;
         if (full) {
+          float m0 = s[0], m1 = s[1], m2 = s[2], m3 = s[3];  // four independent chains
 #pragma unroll
-          for (int i = 0; i < kBN; i += 2) mx = max3(mx, s[i], s[i + 1]);
+          for (int i = 4; i < kBN; i += 8) {
+            m0 = max3(m0, s[i], s[i + 1]);
+            m1 = max3(m1, s[i + 2], s[i + 3]);
+            if (i + 4 < kBN) {
+              m2 = max3(m2, s[i + 4], s[i + 5]);
+              m3 = max3(m3, s[i + 6], s[i + 7]);
+            }
+          }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         } else {
           // hidden columns become -inf, which the exponential below turns into exactly 0
 #pragma unroll
@@ -643,6 +687,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        RAB_TR(w, j, 3);
 
         // P = 2^(s * scale - m_used) two columns at a time (packed fp32x2 multiply-add and
         // add), row sum in two independent accumulators, 16-bit P for the second MMA.
@@ -662,6 +707,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           pk[i / 2 + 1] = pack16<kBf16>(p1.x, p1.y);
         }
         const float row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        RAB_TR(w, j, 4);
         if constexpr (kPInTmem) {
           // keys 0..127 as 64 packed columns over the S columns, which are all consumed by now
           tmem_st32u(t_s, &pk[0]);
@@ -688,6 +734,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tc_fence_before();
         mbar_arrive(bar_p_full + 8 * w);
+        RAB_TR(w, j, 5);
       }
     }
 
@@ -803,9 +850,6 @@ int make_map(CUtensorMap* map, int dtype, const void* base, int D, long long row
 }
 
 int g_p_in_tmem = 1;  // which P path the launcher uses (both are kept buildable and tested)
-// V operand descriptor: 64-element blocks of the head dimension are one 128-row box
-// (16 KiB) apart, 8-key groups 1 KiB apart, one MMA (16 keys) advances 2 KiB.
-unsigned g_v_lbo = kBN * 128, g_v_sbo = 1024, g_v_kstep = 2048;
 
 template <int D, bool kBf16, bool kPInTmem>
 int launch_cfg(const StepArgs& a, cudaStream_t stream) {
@@ -834,9 +878,6 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.flags = a.flags;
   t.doc_len = a.doc_len;
   t.status = a.status;
-  t.v_lbo = g_v_lbo;
-  t.v_sbo = g_v_sbo;
-  t.v_kstep = g_v_kstep;
   const long long n_qblocks = static_cast<long long>(t.n_qblocks_per_seg) * a.qmap.n_seg;
   RAB_REQUIRE(n_qblocks <= 65535, RA_ERR_INVALID, "attention step: too many query blocks (%lld)",
               n_qblocks);
@@ -875,12 +916,19 @@ int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream) {
   return launch_d<128>(dtype, a, stream);
 }
 
+#ifdef RAB_TRACE
+int read_trace(long long* out) {
+  RAB_CUDA(cudaDeviceSynchronize());
+  RAB_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 3 * 64 * 8));
+  return RA_OK;
+}
+#endif
+
 void set_tc_p_in_tmem(int on) { g_p_in_tmem = on ? 1 : 0; }
 
-void set_tc_knob(int which, unsigned value) {
-  if (which == 1) g_v_lbo = value;
-  if (which == 2) g_v_sbo = value;
-  if (which == 3) g_v_kstep = value;
-}
 
 }  // namespace rab
+
+#ifdef RAB_TRACE
+extern "C" RA_API int ra_debug_read_trace(long long* out) { return rab::read_trace(out); }
+#endif
