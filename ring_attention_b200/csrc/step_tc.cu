@@ -328,9 +328,15 @@ struct TcCfg {
   static constexpr int kOffKV = 2 * kTileBytes;
   static constexpr int kOffP = kOffKV + kStages * kTileBytes;
   static constexpr int kOffBar = kOffP + 2 * kPBytes;
-  static constexpr int kNumBars = 2 + 2 * kStages + 6;
+  static constexpr int kNumBars = 2 + 2 * kStages + 8;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + alignment slack
   static constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
+  // P does not overlap S when it lives in shared memory, or in tensor memory at head_dim 64
+  // (S 256 + O 128 + P 128 columns = 512). Then the next S tile can be issued as soon as the
+  // softmax threads hold the current one in registers, instead of after P is written.
+  static constexpr bool kEarlyS = !kPInTmem || D == 64;
+  static constexpr int kColP0 = (kPInTmem && D == 64) ? 384 : kColS0;
+  static constexpr int kColP1 = (kPInTmem && D == 64) ? 448 : kColS1;
 };
 
 struct TileRange {
@@ -394,7 +400,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const unsigned bar_kv_empty = bar_kv_full + 8 * C::kStages;   // [kStages]
   const unsigned bar_s_full = bar_kv_empty + 8 * C::kStages;    // [2]
   const unsigned bar_p_full = bar_s_full + 16;                  // [2]
-  const unsigned bar_o_done = bar_p_full + 16;                  // [2]
+  const unsigned bar_o_done = bar_p_full + 16;                  // [2] PV_w done
+  const unsigned bar_s_free = bar_o_done + 16;                  // [2] S_w held in registers
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + C::kOffBar + C::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -444,6 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_s_full + 8 * w, 1);
       mbar_init(bar_p_full + 8 * w, kBM);
       mbar_init(bar_o_done + 8 * w, 1);
+      mbar_init(bar_s_free + 8 * w, kBM);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -502,6 +510,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr unsigned idesc_pv = make_idesc(kFmt, 1, D, kBM);
       const unsigned t_s[2] = {tmem_base + C::kColS0, tmem_base + C::kColS1};
       const unsigned t_o[2] = {tmem_base + C::kColO0, tmem_base + C::kColO1};
+      [[maybe_unused]] const unsigned t_p[2] = {tmem_base + C::kColP0, tmem_base + C::kColP1};
       // Descriptors are built once; inside the issue loops a descriptor is a base plus a
       // compile-time constant in its 16-byte-unit address field, so the single issuing lane
       // spends a couple of instructions per MMA.
@@ -528,7 +537,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const unsigned long long bd = vd + ks * (2048 >> 4);  // 16 keys = two 8-row groups
           const unsigned accum = (acc || ks > 0) ? 1u : 0u;
           if constexpr (kPInTmem) {
-            mma_ts(t_o[w], t_s[w] + ks * 8, bd, idesc_pv, accum);
+            mma_ts(t_o[w], t_p[w] + ks * 8, bd, idesc_pv, accum);
           } else {
             constexpr unsigned kBox = (kBM * 128) >> 4;
             mma_ss(t_o[w], dp[w] + ((ks / 4) * kBox + (ks % 4) * 2), bd, idesc_pv, accum);
@@ -546,6 +555,42 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_commit(bar_s_full + 8 * w);
       }
       if (ok) tc_commit(bar_kv_empty);
+      if constexpr (C::kEarlyS) {
+        // S_w(j+1) goes out as soon as the softmax threads hold S_w(j) in registers; PV_w(j)
+        // follows when P_w(j) is written. The tensor core works on the next scores while
+        // the exponentials of the current tile run.
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          const int it_v = 2 * j + 1, it_k = 2 * j + 2;
+          const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
+          const bool more = j + 1 < n_tiles;
+          if (more) {
+            ok = mbar_wait(bar_kv_full + 8 * slot_k, (it_k / C::kStages) & 1, abort_flag,
+                           a.status, 5, j);
+            for (int w = 0; w < 2 && ok; ++w) {
+              ok = mbar_wait(bar_s_free + 8 * w, j & 1, abort_flag, a.status, 9, j);
+              if (!ok) break;
+              tc_fence_after();
+              issue_s(w, slot_k);
+              tc_commit(bar_s_full + 8 * w);
+            }
+            if (ok) tc_commit(bar_kv_empty + 8 * slot_k);
+          }
+          if (ok)
+            ok = mbar_wait(bar_kv_full + 8 * slot_v, (it_v / C::kStages) & 1, abort_flag,
+                           a.status, 4, j);
+          for (int w = 0; w < 2 && ok; ++w) {
+            RAB_TR(2, j, 3 * w);
+            ok = mbar_wait(bar_p_full + 8 * w, j & 1, abort_flag, a.status, 6, j);
+            RAB_TR(2, j, 3 * w + 1);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(w, slot_v, j > 0);
+            tc_commit(bar_o_done + 8 * w);
+            RAB_TR(2, j, 3 * w + 2);
+          }
+          if (ok) tc_commit(bar_kv_empty + 8 * slot_v);
+        }
+      } else {
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int it_v = 2 * j + 1, it_k = 2 * j + 2;
         const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
@@ -575,6 +620,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (more) tc_commit(bar_kv_empty + 8 * slot_k);
         }
       }
+      }
     }
   }
   } else {
@@ -585,6 +631,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const unsigned lane_base = static_cast<unsigned>((warp & 3) << 5) << 16;
     const unsigned t_s = tmem_base + lane_base + (w == 0 ? C::kColS0 : C::kColS1);
     const unsigned t_o = tmem_base + lane_base + (w == 0 ? C::kColO0 : C::kColO1);
+    [[maybe_unused]] const unsigned t_p =
+        tmem_base + lane_base + (w == 0 ? C::kColP0 : C::kColP1);
     const int r_in_seg = row0 + w * kBM + row;
     const bool row_valid = r_in_seg < q_seg_len;
     const int qpos = a.qmap.base[sq] + r_in_seg * a.stride;
@@ -638,6 +686,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         // All 128 scores of the row in registers: four loads in flight, one wait.
         float s[kBN];
         tmem_ld128(t_s, s);
+        if constexpr (C::kEarlyS) {
+          // the scores are in registers: the tensor core may overwrite S_w with the next tile
+          tc_fence_before();
+          mbar_arrive(bar_s_free + 8 * w);
+        }
         RAB_TR(w, j, 2);
         float mx = -INFINITY;
         if (full) {
@@ -674,8 +727,19 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           m_used = m_true;
         }
+        if constexpr (C::kEarlyS) {
+          // P_w(j-1) must have been consumed (and O_w must be at rest) before P_w(j) is
+          // written or O_w rescaled: wait for PV_w(j-1). It was issued a whole softmax ago.
+          if (j > 0) {
+            ok = mbar_wait(bar_o_done + 8 * w, (j - 1) & 1, abort_flag, a.status, 10, j);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+          }
+        }
         if (j > 0 && __any_sync(0xffffffffu, rescale)) {
-          // O_w is stable here: S_w(j) was issued after PV_w(j-1) and has completed.
+          // O_w is at rest here: PV_w(j-1) has completed (aliased P: S_w(j) was issued after
+          // it and has completed; separate P: waited for just above).
           l_run *= alpha;
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
@@ -709,9 +773,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         const float row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         RAB_TR(w, j, 4);
         if constexpr (kPInTmem) {
-          // keys 0..127 as 64 packed columns over the S columns, which are all consumed by now
-          tmem_st32u(t_s, &pk[0]);
-          tmem_st32u(t_s + 32, &pk[32]);
+          // keys 0..127 as 64 packed columns (over the consumed S columns when P aliases S)
+          tmem_st32u(t_p, &pk[0]);
+          tmem_st32u(t_p + 32, &pk[32]);
         } else {
           // K-major 128B-swizzled P tile: row r, 16-byte piece q of a 64-key box at
           // r * 128 + ((q ^ (r & 7)) * 16)
@@ -739,7 +803,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ---------------------------------------------------------------- epilogue ----
-    if (ok && n_tiles > 0) ok = mbar_wait(bar_o_done + 8 * w, 0, abort_flag, a.status, 8, n_tiles);
+    if (ok && n_tiles > 0)
+      ok = mbar_wait(bar_o_done + 8 * w, C::kEarlyS ? ((n_tiles - 1) & 1) : 0, abort_flag, a.status,
+                     8, n_tiles);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
