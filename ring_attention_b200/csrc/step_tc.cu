@@ -273,6 +273,31 @@ __device__ inline float2 fadd2(float2 a, float2 b) {
         "l"(*reinterpret_cast<unsigned long long*>(&b)));
   return d;
 }
+// 2^x for two lanes on the FMA pipe: n = round(x) through the 1.5 * 2^23 rounding constant,
+// 2^(x - n) by a degree-3 polynomial on [-0.5, 0.5] (max relative error 7.5e-5, below the
+// 2.4e-4 rounding of 16-bit P), n added to the exponent bits. x is clamped at -125 so that the
+// exponent cannot wrap; 2^-125 becomes 0 when P is rounded to 16 bits.
+#ifndef RAB_POLY_NUM
+#define RAB_POLY_NUM 0
+#define RAB_POLY_DEN 1
+#endif
+constexpr int kPolyNum = RAB_POLY_NUM, kPolyDen = RAB_POLY_DEN;  // share of every second pair
+__device__ inline float2 exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f);
+  const float2 t = fadd2(x, magic);
+  const float2 n = fadd2(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
+  float2 p = ffma2(f, make_float2(0.0551716685f, 0.0551716685f),
+                   make_float2(0.2426111251f, 0.2426111251f));
+  p = ffma2(p, f, make_float2(0.6932609677f, 0.6932609677f));
+  p = ffma2(p, f, make_float2(0.9999280572f, 0.9999280572f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
 template <bool kBf16>
 __device__ inline unsigned pack16(float lo, float hi) {
   if constexpr (kBf16) {
@@ -737,7 +762,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
           }
         }
-        if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+        const bool do_rescale = j > 0 && __any_sync(0xffffffffu, rescale);
+        if (do_rescale) {
           // O_w is at rest here: PV_w(j-1) has completed (aliased P: S_w(j) was issued after
           // it and has completed; separate P: waited for just above).
           l_run *= alpha;
@@ -764,7 +790,15 @@ __global__ void __launch_bounds__(kThreads, 1)
           const float2 x0 = ffma2(make_float2(s[i], s[i + 1]), scale2, negm2);
           const float2 x1 = ffma2(make_float2(s[i + 2], s[i + 3]), scale2, negm2);
           const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
-          const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
+          // The exp unit does 16 results per clock per SM, half the rate the tensor core
+          // needs at these tile sizes, so part of the exponentials is computed on the FMA
+          // pipe instead (kPolyNum of every kPolyDen pairs of this stream).
+          float2 p1;
+          if ((i / 4) % kPolyDen < kPolyNum) {
+            p1 = exp2_poly2(x1);
+          } else {
+            p1 = make_float2(ex2(x1.x), ex2(x1.y));
+          }
           sum_a = fadd2(sum_a, p0);
           sum_b = fadd2(sum_b, p1);
           pk[i / 2] = pack16<kBf16>(p0.x, p0.y);
@@ -812,7 +846,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       const size_t grow = (static_cast<size_t>(bh) * a.Sq + static_cast<size_t>(sq) * q_seg_len +
                            (row_valid ? r_in_seg : 0));
       float* o_g = a.out + grow * D;
-      const bool have = row_valid && n_tiles > 0 && l_run > 0.f;
+      // (the polynomial exponential turns a hidden score into 2^-125, not 0, so "saw a key"
+      // is read off the running maximum, not off the sum)
+      const bool have = row_valid && n_tiles > 0 && m_true > -INFINITY;
       float m_old = -INFINITY, l_old = 0.f;
       if (!fresh && row_valid) {
         m_old = a.m[grow];
