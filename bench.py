@@ -238,15 +238,14 @@ def run_gpu_arm(args):
             host_out.copy_(out, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to start: begin before the warm-up
     for _ in range(max(args.warmup, 3)):
         flush.fill_(1)
         one_pass()
     barrier()
     assert api.device_status()[0] == 0, "a device-side wait ran out during warm-up"
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     K = max(1, args.steps)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     barrier()

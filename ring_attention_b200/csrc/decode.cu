@@ -16,6 +16,11 @@
 //    the end, where a warp-shuffle log-sum-exp merge and one shared-memory pass combine the
 //    lane groups and warps of the block.
 //  - The split count is chosen so the grid is about three waves of the SM count.
+//  - fp16 / bf16 caches with head_dim >= 64 take the tensor-core kernel further down
+//    (decode_mma_kernel): the same streaming structure with the two contractions of each
+//    16-key block on mma.sync, because the SIMT form is bound by instruction issue (about 80
+//    warp instructions per cached row) at 43 % of HBM speed, the MMA form by the copy (87 %).
+//    fp32 caches and head_dim 32 keep the SIMT kernel.
 // Partials (m, l, out) per (split, batch, head) go to a workspace; a second tiny kernel
 // folds them into the persistent state (src/attention_decode.cu:228-277 does the same for
 // its fixed 8 splits).
@@ -315,6 +320,281 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// ---- tensor-core variant for 16-bit caches ---------------------------------------------
+//
+// The SIMT kernel above spends ~80 warp instructions per cached row (a convert and one FMA
+// per element per query head), which makes it issue-bound at well under HBM speed. For
+// fp16 / bf16 caches both contractions of a block of 16 keys run on mma.sync m16n8k16
+// instead: the (up to 16) query heads that share the KV head are the M rows, so a key row
+// costs ~5 instructions and the kernel is bound by the copy into shared memory again.
+// K/V rows go to shared memory with the same 16-byte cp.async copies, but each 16-byte
+// piece c of row r is stored at piece c ^ (r & 7), so that the ldmatrix reads (8 rows at a
+// fixed column) touch all banks once.
+constexpr int kMmaWarps = 4;
+constexpr int kMmaThreads = kMmaWarps * 32;
+constexpr int kMmaKeysPerWarp = 16;
+constexpr int kMmaStageRows = kMmaWarps * kMmaKeysPerWarp;  // 64 keys per stage
+
+template <typename T>
+__device__ inline void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1);
+template <>
+__device__ inline void mma16816<__half>(float (&c)[4], const unsigned (&a)[4], unsigned b0,
+                                        unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ inline void mma16816<__nv_bfloat16>(float (&c)[4], const unsigned (&a)[4], unsigned b0,
+                                               unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ inline void ldmatrix_x4(unsigned (&r)[4], unsigned saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(saddr));
+}
+__device__ inline void ldmatrix_x4_trans(unsigned (&r)[4], unsigned saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(saddr));
+}
+template <typename T>
+__device__ inline unsigned pack_pair(float lo, float hi);
+template <>
+__device__ inline unsigned pack_pair<__half>(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&h);
+}
+template <>
+__device__ inline unsigned pack_pair<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&h);
+}
+
+template <int D>
+struct MmaCfg {
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kPieces = kRowBytes / 16;
+  static constexpr int kStageBytes = kMmaStageRows * kRowBytes;  // per tensor
+  static constexpr int kStagesRaw = (160 * 1024) / (2 * kStageBytes);
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : (kStagesRaw < 3 ? 3 : kStagesRaw);
+  static constexpr int kSmemBytes = 2 * kStages * kStageBytes;
+};
+
+// grid = (n_split, kv_heads * head_batches, batch); a block serves up to 16 query heads of one
+// KV head (rows of the MMA tile; row r is head kvh + kv_heads * (16 * hb + r)).
+template <typename T, int D>
+__global__ void __launch_bounds__(kMmaThreads)
+    decode_mma_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
+                      float* __restrict__ Mp, float* __restrict__ Lp, float* __restrict__ Op, int B,
+                      int H, int kvH, int sk_eff, long long kv_head_stride, int rows_per_split,
+                      int head_batches, float scale_log2) {
+  using C = MmaCfg<D>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* k_ring = smem;
+  unsigned char* v_ring = smem + C::kStages * C::kStageBytes;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int g = lane >> 2;   // fragment row (and row + 8)
+  const int tq = lane & 3;   // fragment column pair
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / head_batches;
+  const int hb = blockIdx.y % head_batches;
+  const int b = blockIdx.z;
+
+  // Q as A fragments: reg0 (row g, k 2tq..), reg1 (row g+8, same k), reg2 / reg3 the same at k+8.
+  const int h0 = kvh + kvH * (hb * 16 + g);
+  const int h1 = kvh + kvH * (hb * 16 + g + 8);
+  unsigned qa[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const int d0 = ks * 16 + 2 * tq;
+    const T* q0 = Q + (static_cast<size_t>(b) * H + (h0 < H ? h0 : 0)) * D + d0;
+    const T* q1 = Q + (static_cast<size_t>(b) * H + (h1 < H ? h1 : 0)) * D + d0;
+    qa[ks][0] = h0 < H ? *reinterpret_cast<const unsigned*>(q0) : 0u;
+    qa[ks][1] = h1 < H ? *reinterpret_cast<const unsigned*>(q1) : 0u;
+    qa[ks][2] = h0 < H ? *reinterpret_cast<const unsigned*>(q0 + 8) : 0u;
+    qa[ks][3] = h1 < H ? *reinterpret_cast<const unsigned*>(q1 + 8) : 0u;
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};  // this lane's share of the row sums (its four columns per block)
+
+  const int row_begin = split * rows_per_split;
+  const int row_end = min(sk_eff, row_begin + rows_per_split);
+  const int n_rows = max(0, row_end - row_begin);
+  const int n_stages = (n_rows + kMmaStageRows - 1) / kMmaStageRows;
+  const unsigned char* k_base = reinterpret_cast<const unsigned char*>(
+      K + (static_cast<size_t>(b) * kvH + kvh) * kv_head_stride);
+  const unsigned char* v_base = reinterpret_cast<const unsigned char*>(
+      V + (static_cast<size_t>(b) * kvH + kvh) * kv_head_stride);
+
+  auto issue = [&](int st) {
+    if (st < n_stages) {
+      const int slot = st % C::kStages;
+      const long long first = static_cast<long long>(row_begin) + st * kMmaStageRows;
+      const long long valid_bytes = (static_cast<long long>(row_end) - first) * C::kRowBytes;
+      const size_t goff = static_cast<size_t>(first) * C::kRowBytes;
+      for (int p = tid; p < C::kStageBytes / 16; p += kMmaThreads) {
+        const int r = p / C::kPieces;
+        const int c = p - r * C::kPieces;
+        const long long off = static_cast<long long>(p) * 16;
+        const int dst = slot * C::kStageBytes + r * C::kRowBytes + ((c ^ (r & 7)) << 4);
+        const bool ok = off < valid_bytes;
+        cp_async16(k_ring + dst, ok ? k_base + goff + off : k_base, ok ? 16 : 0);
+        cp_async16(v_ring + dst, ok ? v_base + goff + off : v_base, ok ? 16 : 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int s = 0; s < C::kStages - 1; ++s) issue(s);
+
+  const int mi = lane >> 3, r8 = lane & 7;
+  const int key0 = warp * kMmaKeysPerWarp;
+  // per-lane row offsets of the ldmatrix addresses (piece index is XORed with r8 = key & 7)
+  const unsigned k_row_off = static_cast<unsigned>((key0 + (mi >> 1) * 8 + r8) * C::kRowBytes);
+  const unsigned v_row_off = static_cast<unsigned>((key0 + (mi & 1) * 8 + r8) * C::kRowBytes);
+
+  for (int st = 0; st < n_stages; ++st) {
+    cp_async_wait<C::kStages - 2>();
+    __syncthreads();
+    issue(st + C::kStages - 1);
+    const int slot = st % C::kStages;
+    const int n_valid = n_rows - (st * kMmaStageRows + key0);  // valid keys of this warp's block
+    if (n_valid <= 0) continue;
+    const unsigned kt = static_cast<unsigned>(__cvta_generic_to_shared(k_ring + slot * C::kStageBytes));
+    const unsigned vt = static_cast<unsigned>(__cvta_generic_to_shared(v_ring + slot * C::kStageBytes));
+
+    // S = Q K^T for 16 keys: s0 = keys 0..7, s1 = keys 8..15
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      unsigned kb[4];
+      ldmatrix_x4(kb, kt + k_row_off + (((2 * ks + (mi & 1)) ^ r8) << 4));
+      mma16816<T>(s0, qa[ks], kb[0], kb[1]);
+      mma16816<T>(s1, qa[ks], kb[2], kb[3]);
+    }
+    // scale, hide the keys past the end, row maxima (rows g and g + 8)
+    float v[8] = {s0[0], s0[1], s1[0], s1[1], s0[2], s0[3], s1[2], s1[3]};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int col = ((i >> 1) & 1) * 8 + 2 * tq + (i & 1);
+      v[i] = (col < n_valid) ? v[i] * scale_log2 : -INFINITY;
+    }
+    float mx0 = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+    float mx1 = fmaxf(fmaxf(v[4], v[5]), fmaxf(v[6], v[7]));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const bool moved = mx0 > m_run[0] || mx1 > m_run[1];
+    if (__any_sync(0xffffffffu, moved)) {  // rare after the first blocks
+      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+      const float a0 = (m_run[0] == -INFINITY) ? 0.f : ex2(m_run[0] - mn0);
+      const float a1 = (m_run[1] == -INFINITY) ? 0.f : ex2(m_run[1] - mn1);
+      l_run[0] *= a0;
+      l_run[1] *= a1;
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        o[n][0] *= a0;
+        o[n][1] *= a0;
+        o[n][2] *= a1;
+        o[n][3] *= a1;
+      }
+      m_run[0] = mn0;
+      m_run[1] = mn1;
+    }
+    const float ms0 = (m_run[0] == -INFINITY) ? 0.f : m_run[0];
+    const float ms1 = (m_run[1] == -INFINITY) ? 0.f : m_run[1];
+    float p[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      p[i] = ex2(v[i] - ms0);
+      p[4 + i] = ex2(v[4 + i] - ms1);
+    }
+    l_run[0] += (p[0] + p[1]) + (p[2] + p[3]);
+    l_run[1] += (p[4] + p[5]) + (p[6] + p[7]);
+    // P as the A fragment of the second product
+    unsigned pa[4];
+    pa[0] = pack_pair<T>(p[0], p[1]);  // row g,     keys 2tq, 2tq+1
+    pa[1] = pack_pair<T>(p[4], p[5]);  // row g + 8, same keys
+    pa[2] = pack_pair<T>(p[2], p[3]);  // row g,     keys 8 + 2tq, ...
+    pa[3] = pack_pair<T>(p[6], p[7]);  // row g + 8
+#pragma unroll
+    for (int c2 = 0; c2 < D / 16; ++c2) {
+      unsigned vb[4];
+      ldmatrix_x4_trans(vb, vt + v_row_off + (((2 * c2 + (mi >> 1)) ^ r8) << 4));
+      mma16816<T>(o[2 * c2], pa, vb[0], vb[1]);
+      mma16816<T>(o[2 * c2 + 1], pa, vb[2], vb[3]);
+    }
+  }
+  cp_async_wait<0>();
+
+  // row sums over the four lanes of a row, then the warps of the block through shared memory
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+  }
+  __syncthreads();
+  float* red_m = reinterpret_cast<float*>(smem);  // [warps][16]
+  float* red_l = red_m + kMmaWarps * 16;          // [warps][16]
+  float* red_o = red_l + kMmaWarps * 16;          // [warps][16][D]
+  if (tq == 0) {
+    red_m[warp * 16 + g] = m_run[0];
+    red_m[warp * 16 + g + 8] = m_run[1];
+    red_l[warp * 16 + g] = l_run[0];
+    red_l[warp * 16 + g + 8] = l_run[1];
+  }
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) {
+    float* r0 = red_o + (warp * 16 + g) * D + n * 8 + 2 * tq;
+    float* r1 = red_o + (warp * 16 + g + 8) * D + n * 8 + 2 * tq;
+    r0[0] = o[n][0];
+    r0[1] = o[n][1];
+    r1[0] = o[n][2];
+    r1[1] = o[n][3];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < 16 * D; idx += kMmaThreads) {
+    const int r = idx / D;
+    const int d = idx - r * D;
+    const int h = kvh + kvH * (hb * 16 + r);
+    if (h >= H) continue;
+    float m_n = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) m_n = fmaxf(m_n, red_m[w * 16 + r]);
+    float o_acc = 0.f, l_acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) {
+      const float mw = red_m[w * 16 + r];
+      const float sc = (mw == -INFINITY) ? 0.f : ex2(mw - m_n);
+      o_acc += sc * red_o[(w * 16 + r) * D + d];
+      l_acc += sc * red_l[w * 16 + r];
+    }
+    const size_t prow = (static_cast<size_t>(split) * B + b) * H + h;
+    Op[prow * D + d] = o_acc;
+    if (d == 0) {
+      Mp[prow] = m_n * kLn2;
+      Lp[prow] = l_acc;
+    }
+  }
+}
+
 // Fold n_split partials into the persistent (out, m, l). grid = (H, B), block = D threads.
 __global__ void decode_reduce_kernel(const float* __restrict__ Mp, const float* __restrict__ Lp,
                                      const float* __restrict__ Op, float* __restrict__ M,
@@ -407,6 +687,46 @@ int launch_decode_typed(const void* q, const void* k, const void* v, float* out,
                         float* l, const ra_shape& s, int sk_eff, long long kv_head_stride,
                         void* workspace, size_t workspace_bytes, cudaStream_t stream,
                         int split_cap = kMaxSplits) {
+  if constexpr (sizeof(T) == 2 && D >= 64) {
+    // 16-bit caches: the tensor-core kernel (16 query heads per block, 64-key stages)
+    using M = MmaCfg<D>;
+    const int kvH = kv_heads_of(s);
+    const int group = (s.heads + kvH - 1) / kvH;
+    const int head_batches = (group + 15) / 16;
+    const int blocks_per_split = s.batch * kvH * head_batches;
+    int want = (3 * sm_count() + blocks_per_split - 1) / blocks_per_split;
+    want = std::max(1, std::min(std::min(want, std::max(1, sk_eff / (2 * kMmaStageRows))),
+                                split_cap));
+    int rps = (sk_eff + want - 1) / want;
+    rps = ((rps + kMmaStageRows - 1) / kMmaStageRows) * kMmaStageRows;
+    const int n_split = std::max(1, (sk_eff + rps - 1) / rps);
+    const size_t prow = static_cast<size_t>(n_split) * s.batch * s.heads;
+    const size_t need = prow * (D + 2) * sizeof(float);
+    if (workspace == nullptr) {
+      const int rc = ensure_workspace(need, &workspace);
+      if (rc != RA_OK) return rc;
+    } else {
+      RAB_REQUIRE(workspace_bytes >= need, RA_ERR_OVERFLOW,
+                  "decode workspace too small: %zu < %zu bytes", workspace_bytes, need);
+    }
+    float* Mp = static_cast<float*>(workspace);
+    float* Lp = Mp + prow;
+    float* Op = Lp + prow;
+    const float scale_log2 = kLog2e / sqrtf(static_cast<float>(D));
+    const size_t red_bytes = static_cast<size_t>(kMmaWarps) * 16 * (D + 2) * sizeof(float);
+    const size_t smem = std::max(static_cast<size_t>(M::kSmemBytes), red_bytes);
+    auto kern = decode_mma_kernel<T, D>;
+    RAB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
+    kern<<<dim3(n_split, kvH * head_batches, s.batch), kMmaThreads, smem, stream>>>(
+        static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), Mp, Lp, Op,
+        s.batch, s.heads, kvH, sk_eff, kv_head_stride, rps, head_batches, scale_log2);
+    RAB_CUDA(cudaGetLastError());
+    decode_reduce_kernel<<<dim3(s.heads, s.batch), D, 0, stream>>>(Mp, Lp, Op, m, l, out, s.batch,
+                                                                   s.heads, D, n_split);
+    RAB_CUDA(cudaGetLastError());
+    return RA_OK;
+  }
   using C = DecodeCfg<T, D>;
   const int kvH = kv_heads_of(s);
   const Plan p =
