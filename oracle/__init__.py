@@ -25,6 +25,15 @@ def build(verbose: bool = False) -> None:
         print(r.stdout, r.stderr)
     if r.returncode != 0:
         raise RuntimeError("oracle build failed")
+    # the reference's own test programs against the product library (needs the library built
+    # and the reference tree mounted; otherwise prebuilt binaries are kept)
+    lib = os.path.join(_HERE, "..", "ring_attention_b200", "libring_attention_b200.so")
+    if os.path.exists(lib):
+        r = subprocess.run(["make", "-C", _HERE, "reftests"], capture_output=True, text=True)
+        if verbose or r.returncode != 0:
+            print(r.stdout[-3000:], r.stderr[-3000:])
+        if r.returncode != 0:
+            raise RuntimeError("building the reference's test programs failed")
 
 
 def _load(path):
