@@ -299,6 +299,15 @@ RA_API int ra_ring_decode_step(ra_ring* r, int batch, int heads, const void* q, 
                                const int* current_len_per_rank, float* out, ra_stream stream,
                                ra_ring_result* result);
 
+/* The same step on raw cache pointers (K, V of shape (batch, kv_heads, s_max, head_dim), the
+ * first local_len rows of every head valid), for callers that own the cache themselves, such
+ * as the reference's DeviceKVCache<T> (src/kv_cache.hpp:22-73); the append on the owner rank
+ * is then the caller's (src/ring_decode.cu:116-118). */
+RA_API int ra_ring_decode_step_raw(ra_ring* r, int dtype, int batch, int heads, int kv_heads,
+                                   int head_dim, const void* q, const void* k_cache,
+                                   const void* v_cache, int local_len, int s_max, float* out,
+                                   ra_stream stream, ra_ring_result* result);
+
 #ifdef __cplusplus
 }
 #endif

@@ -126,6 +126,8 @@ _SIG = {
                                   _P, C.POINTER(RingResult)]),
     "ra_ring_decode_step": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_int, _P,
                                       C.POINTER(C.c_int), _P, _P, C.POINTER(RingResult)]),
+    "ra_ring_decode_step_raw": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P,
+                                          C.c_int, C.c_int, _P, _P, C.POINTER(RingResult)]),
     "ra_debug_set_p_in_tmem": (None, [C.c_int]),
 }
 

@@ -302,27 +302,15 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
   return RA_OK;
 }
 
-int ra_ring_decode_step(ra_ring* r, int batch, int heads, const void* q, const void* k_new,
-                        const void* v_new, int owner_rank, ra_kv_cache* cache,
-                        const int* current_len_per_rank, float* out, ra_stream stream_,
-                        ra_ring_result* result) {
-  RAB_REQUIRE(r && q && cache && current_len_per_rank && out, RA_ERR_INVALID,
-              "ring decode: null argument");
-  RAB_REQUIRE(owner_rank >= 0 && owner_rank < r->cp, RA_ERR_INVALID,
-              "ring decode: owner_rank %d out of range", owner_rank);
-  RAB_REQUIRE(batch == cache->batch, RA_ERR_INVALID, "ring decode: batch %d != cache batch %d",
-              batch, cache->batch);
+int ra_ring_decode_step_raw(ra_ring* r, int dtype, int batch, int heads, int kv_heads,
+                            int head_dim, const void* q, const void* k_cache, const void* v_cache,
+                            int local_len, int s_max, float* out, ra_stream stream_,
+                            ra_ring_result* result) {
+  RAB_REQUIRE(r && q && k_cache && v_cache && out, RA_ERR_INVALID, "ring decode: null argument");
+  RAB_REQUIRE(batch > 0 && heads > 0 && local_len >= 0 && local_len <= s_max, RA_ERR_INVALID,
+              "ring decode: bad sizes (local_len=%d, s_max=%d)", local_len, s_max);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const int D = cache->head_dim;
-  if (r->rank == owner_rank) {
-    RAB_REQUIRE(k_new && v_new, RA_ERR_INVALID, "ring decode: owner needs k_new / v_new");
-    const int rc = ra_kv_cache_append(cache, k_new, v_new, stream_);
-    if (rc != RA_OK) return rc;
-  }
-  // the caller's bookkeeping must agree with the cache (src/ring_decode.cu:108-125)
-  RAB_REQUIRE(current_len_per_rank[r->rank] == cache->current_len, RA_ERR_INVALID,
-              "ring_decode: current_len_per_rank[%d]=%d but cache.current_len=%d", r->rank,
-              current_len_per_rank[r->rank], cache->current_len);
+  const int D = head_dim;
   const size_t bh = static_cast<size_t>(batch) * heads;
   const size_t block = bh * D + 2 * bh;  // floats per rank: [O | m | l]
   const size_t need = (1 + static_cast<size_t>(r->cp)) * block * sizeof(float);
@@ -341,12 +329,11 @@ int ra_ring_decode_step(ra_ring* r, int batch, int heads, const void* q, const v
   RAB_CUDA(cudaEventRecord(r->ev_start, stream));
   int rc = launch_init(o_p, m_p, l_p, bh * D, bh, stream);
   if (rc != RA_OK) return rc;
-  const int local_len = cache->current_len;
   if (local_len > 0) {
-    ra_shape s{batch, heads, 1, local_len, D, cache->kv_heads};
+    ra_shape s{batch, heads, 1, local_len, D, kv_heads};
     // causality is implicit: the cache only ever holds past tokens (src/ring_decode.cu:173-175)
-    rc = decode_step(cache->dtype, q, cache->k, cache->v, o_p, m_p, l_p, s, 0, 0, 0, stream,
-                     cache->s_max, nullptr, 0);
+    rc = decode_step(dtype, q, k_cache, v_cache, o_p, m_p, l_p, s, 0, 0, 0, stream, s_max, nullptr,
+                     0);
     if (rc != RA_OK) return rc;
   }
   RAB_CUDA(cudaEventRecord(r->ev_comp[0], stream));
@@ -372,6 +359,30 @@ int ra_ring_decode_step(ra_ring* r, int batch, int heads, const void* q, const v
     result->total_ms = t;
   }
   return RA_OK;
+}
+
+int ra_ring_decode_step(ra_ring* r, int batch, int heads, const void* q, const void* k_new,
+                        const void* v_new, int owner_rank, ra_kv_cache* cache,
+                        const int* current_len_per_rank, float* out, ra_stream stream_,
+                        ra_ring_result* result) {
+  RAB_REQUIRE(r && q && cache && current_len_per_rank && out, RA_ERR_INVALID,
+              "ring decode: null argument");
+  RAB_REQUIRE(owner_rank >= 0 && owner_rank < r->cp, RA_ERR_INVALID,
+              "ring decode: owner_rank %d out of range", owner_rank);
+  RAB_REQUIRE(batch == cache->batch, RA_ERR_INVALID, "ring decode: batch %d != cache batch %d",
+              batch, cache->batch);
+  if (r->rank == owner_rank) {
+    RAB_REQUIRE(k_new && v_new, RA_ERR_INVALID, "ring decode: owner needs k_new / v_new");
+    const int rc = ra_kv_cache_append(cache, k_new, v_new, stream_);
+    if (rc != RA_OK) return rc;
+  }
+  // the caller's bookkeeping must agree with the cache (src/ring_decode.cu:108-125)
+  RAB_REQUIRE(current_len_per_rank[r->rank] == cache->current_len, RA_ERR_INVALID,
+              "ring_decode: current_len_per_rank[%d]=%d but cache.current_len=%d", r->rank,
+              current_len_per_rank[r->rank], cache->current_len);
+  return ra_ring_decode_step_raw(r, cache->dtype, batch, heads, cache->kv_heads, cache->head_dim, q,
+                                 cache->k, cache->v, cache->current_len, cache->s_max, out, stream_,
+                                 result);
 }
 
 }  // extern "C"

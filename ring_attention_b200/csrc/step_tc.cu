@@ -257,6 +257,9 @@ __device__ inline float max3(float a, float b, float c) {
 }
 // packed fp32x2 arithmetic: one instruction for two lanes of a float2
 __device__ inline float2 ffma2(float2 a, float2 b, float2 c) {
+#ifdef RAB_SCALAR_MATH
+  return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
+#endif
   float2 d;
   asm("fma.rn.f32x2 %0, %1, %2, %3;"
       : "=l"(*reinterpret_cast<unsigned long long*>(&d))
@@ -266,6 +269,9 @@ __device__ inline float2 ffma2(float2 a, float2 b, float2 c) {
   return d;
 }
 __device__ inline float2 fadd2(float2 a, float2 b) {
+#ifdef RAB_SCALAR_MATH
+  return make_float2(a.x + b.x, a.y + b.y);
+#endif
   float2 d;
   asm("add.rn.f32x2 %0, %1, %2;"
       : "=l"(*reinterpret_cast<unsigned long long*>(&d))
@@ -277,6 +283,12 @@ __device__ inline float2 fadd2(float2 a, float2 b) {
 // 2^(x - n) by a degree-3 polynomial on [-0.5, 0.5] (max relative error 7.5e-5, below the
 // 2.4e-4 rounding of 16-bit P), n added to the exponent bits. x is clamped at -125 so that the
 // exponent cannot wrap; 2^-125 becomes 0 when P is rounded to 16 bits.
+// Register split between the producer / MMA warpgroup and the two softmax warpgroups
+// (128 * LO + 256 * HI <= 65536).
+#ifndef RAB_REGS_LO
+#define RAB_REGS_LO 72
+#define RAB_REGS_HI 216
+#endif
 #ifndef RAB_POLY_NUM
 #define RAB_POLY_NUM 0
 #define RAB_POLY_DEN 1
@@ -300,6 +312,9 @@ __device__ inline float2 exp2_poly2(float2 x) {
 }
 template <bool kBf16>
 __device__ inline unsigned pack16(float lo, float hi) {
+#ifdef RAB_NO_PACK
+  return __float_as_uint(lo) ^ __float_as_uint(hi);  // timing experiment only
+#endif
   if constexpr (kBf16) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned*>(&h);
@@ -312,6 +327,9 @@ __device__ inline void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ inline float ex2(float x) {
+#ifdef RAB_EXP_FAKE
+  return fmaf(x, x, 1.0f);  // timing experiment only
+#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -495,7 +513,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // Registers follow the work: the producer / MMA warpgroup gives most of its registers back,
   // the two softmax warpgroups (one row of 128 scores per thread) take them.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(RAB_REGS_LO));
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ----
     if (lane == 0 && n_tiles > 0) {
@@ -649,7 +667,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(RAB_REGS_HI));
     // ----------------------------------------------------------------- softmax ----
     const int w = (warp - 4) >> 2;                   // query tile of this warpgroup
     const int row = ((warp & 3) << 5) + lane;        // row inside the tile = TMEM lane
@@ -738,6 +756,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             mx = fmaxf(mx, s[i]);
           }
         }
+        RAB_TR(w, j, 6);
         const float tile_max = mx * scale_log2;  // -inf stays -inf (scale > 0)
         m_true = fmaxf(m_true, tile_max);
         // Move the reference point only when it is unset or the max moved by more than the
@@ -762,6 +781,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
           }
         }
+        RAB_TR(w, j, 7);
         const bool do_rescale = j > 0 && __any_sync(0xffffffffu, rescale);
         if (do_rescale) {
           // O_w is at rest here: PV_w(j-1) has completed (aliased P: S_w(j) was issued after

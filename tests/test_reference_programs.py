@@ -39,3 +39,65 @@ def test_reference_gpu_programs(name, expect):
     if expect:
         assert expect in out
     assert "FAIL" not in out
+
+
+# ---- the reference's MPI programs (its CTest smoke matrix, tests/CMakeLists.txt:22-60,108-177) ----
+
+def mpirun(n, prog, *args, timeout=600):
+    import torch
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    launcher, path = os.path.join(BIN, "mpirun"), os.path.join(BIN, prog)
+    if not (os.path.exists(launcher) and os.path.exists(path)):
+        pytest.skip(f"{prog} was not built (oracle/_ref/tests is made where the reference tree is mounted)")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MINIMPI_TIMEOUT_S="120")
+    r = subprocess.run([launcher, "-n", str(n), path, *args], capture_output=True, text=True, timeout=timeout,
+                       env=env)
+    assert r.returncode == 0, f"{prog} {args} failed:\n{r.stdout[-2000:]}\n{r.stderr[-2000:]}"
+    return r.stdout
+
+
+SMOKE = ["--seq", "128", "--heads", "2", "--head_dim", "32", "--iters", "1", "--causal", "1"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1, 2, 4])
+@pytest.mark.parametrize("mode,extra", [
+    ("allgather", ["--zigzag", "0"]), ("ring-blocking", ["--zigzag", "1"]), ("ring-overlap", ["--zigzag", "1"]),
+    ("ring-2d", ["--zigzag", "1"]), ("ring-overlap", ["--striped"]), ("ring-overlap", ["--zigzag-n", "2"]),
+    ("ring-overlap", ["--zigzag-n", "2", "--segmented"]),
+    ("allgather", ["--zigzag", "0", "--dtype", "fp16"]), ("ring-blocking", ["--zigzag", "1", "--dtype", "fp16"]),
+    ("ring-overlap", ["--zigzag", "1", "--dtype", "fp16"]), ("ring-overlap", ["--striped", "--dtype", "fp16"])])
+def test_reference_cli_ring_smoke(n, mode, extra):
+    import re
+    out = mpirun(n, "ring_attention_cli", *SMOKE, *extra, "--mode", mode, "--verify")
+    assert re.search(r"verify[^\n]*PASS", out), out[-1500:]
+
+
+@pytest.mark.gpu
+def test_reference_cli_larger_shapes_verify():
+    import re
+    for args in (["--seq", "1024", "--heads", "4", "--kv_heads", "2", "--head_dim", "64", "--dtype", "fp16",
+                  "--zigzag", "1"],
+                 ["--seq", "512", "--heads", "4", "--head_dim", "128", "--dtype", "fp16", "--striped"],
+                 ["--seq", "512", "--heads", "2", "--head_dim", "128", "--zigzag-n", "2"]):
+        out = mpirun(2, "ring_attention_cli", *args, "--iters", "2", "--causal", "1", "--mode", "ring-overlap",
+                     "--verify")
+        assert re.search(r"verify[^\n]*PASS", out), out[-1500:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,dim", [(2, 32), (2, 64), (4, 32)])
+def test_reference_ring_decode_program(n, dim):
+    import re
+    out = mpirun(n, "test_ring_decode", "--prompt_len", "32", "--n_decode", "4", "--batch", "1", "--heads", "2",
+                 "--head_dim", str(dim))
+    assert re.search(r"ring_decode[^\n]*PASS", out), out[-1500:]
+
+
+@pytest.mark.gpu
+def test_reference_cli_decode_benchmark_csv():
+    import re
+    out = mpirun(2, "ring_attention_cli", "--run", "decode", "--prompt-len", "64", "--decode-tokens", "3",
+                 "--batch", "1", "--heads", "2", "--head_dim", "32", "--csv-header", "--csv")
+    assert re.search(r"decode summary[^\n]*cp_size=2", out), out[-1500:]
