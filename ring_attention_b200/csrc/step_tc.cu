@@ -257,9 +257,6 @@ __device__ inline float max3(float a, float b, float c) {
 }
 // packed fp32x2 arithmetic: one instruction for two lanes of a float2
 __device__ inline float2 ffma2(float2 a, float2 b, float2 c) {
-#ifdef RAB_SCALAR_MATH
-  return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
-#endif
   float2 d;
   asm("fma.rn.f32x2 %0, %1, %2, %3;"
       : "=l"(*reinterpret_cast<unsigned long long*>(&d))
@@ -269,9 +266,6 @@ __device__ inline float2 ffma2(float2 a, float2 b, float2 c) {
   return d;
 }
 __device__ inline float2 fadd2(float2 a, float2 b) {
-#ifdef RAB_SCALAR_MATH
-  return make_float2(a.x + b.x, a.y + b.y);
-#endif
   float2 d;
   asm("add.rn.f32x2 %0, %1, %2;"
       : "=l"(*reinterpret_cast<unsigned long long*>(&d))
@@ -312,9 +306,7 @@ __device__ inline float2 exp2_poly2(float2 x) {
 }
 template <bool kBf16>
 __device__ inline unsigned pack16(float lo, float hi) {
-#ifdef RAB_NO_PACK
-  return __float_as_uint(lo) ^ __float_as_uint(hi);  // timing experiment only
-#endif
+
   if constexpr (kBf16) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned*>(&h);
@@ -327,9 +319,6 @@ __device__ inline void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ inline float ex2(float x) {
-#ifdef RAB_EXP_FAKE
-  return fmaf(x, x, 1.0f);  // timing experiment only
-#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -810,9 +799,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           const float2 x0 = ffma2(make_float2(s[i], s[i + 1]), scale2, negm2);
           const float2 x1 = ffma2(make_float2(s[i + 2], s[i + 3]), scale2, negm2);
           const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
-          // The exp unit does 16 results per clock per SM, half the rate the tensor core
-          // needs at these tile sizes, so part of the exponentials is computed on the FMA
-          // pipe instead (kPolyNum of every kPolyDen pairs of this stream).
+          // Optionally (kPolyNum of every kPolyDen pairs of this stream) the exponential is
+          // computed on the FMA pipe instead of the exp unit. Off by default: measured on
+          // B200 it does not pay, because with the exp unit relieved the chain of the single
+          // MMA-issuing lane (wait, issue, complete, wake) bounds the tile period at about the
+          // same length.
           float2 p1;
           if ((i / 4) % kPolyDen < kPolyNum) {
             p1 = exp2_poly2(x1);
