@@ -41,6 +41,22 @@ sys.path.insert(0, ROOT)
 
 WORKLOAD = dict(batch=1, heads=8, kv_heads=8, seq=32768, head_dim=64, dtype="fp16", causal=True,
                 layout="zigzag", n_splits=2)
+# The benchmark line is config 2 (the workload the metric is quoted on). The other prefill
+# workloads of the same metric can be run with --workload for the scaling tables; they keep the
+# same JSON contract and say which workload they are in config.workload.
+WORKLOADS = {
+    "config2": dict(WORKLOAD, name="causal zig-zag ring-overlap prefill fp16 B1 S32768 H8 D64 (config 2)",
+                    scale=1.0, doc_len=0, seq_per_gpu=None),
+    "config3": dict(batch=2, heads=32, kv_heads=8, seq=131072, head_dim=128, dtype="fp16", causal=True,
+                    layout="striped", n_splits=2, scale=0.5, doc_len=0, seq_per_gpu=None,
+                    name="causal GQA striped ring-overlap prefill fp16 B2 S131072 H32/kvH8 D128 (config 3)"),
+    # 1 M tokens on 8 GPUs, 512 K on 4: 131072 tokens per GPU, four equal documents
+    "config5": dict(batch=1, heads=16, kv_heads=16, seq=None, head_dim=128, dtype="fp16", causal=True,
+                    layout="zigzag", n_splits=4, scale=1.0, doc_len="seq/4", seq_per_gpu=131072,
+                    name="long-context causal prefill fp16 B1 H16 D128, zig-zag-n=2, 4 documents, "
+                         "131072 tokens per GPU (config 5: 1048576 tokens on 8 GPUs)"),
+}
+LAYOUTS = {"contiguous": 0, "zigzag": 1, "striped": 2}
 DECODE = dict(batch=4, heads=32, kv_heads=8, head_dim=128, prompt=262144, dtype="fp16")
 METRIC = "causal-adjusted attention TFLOP/s (prefill, whole job)"
 
@@ -195,17 +211,31 @@ def run_gpu_arm(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     P = world
-    w = WORKLOAD
-    B, H, S, D = w["batch"], w["heads"], w["seq"], w["head_dim"]
-    part = api.RingPartition(P, rank, S, api.RingPartition.ZIGZAG, w["n_splits"])
+    w = dict(WORKLOADS[args.workload])
+    if w["seq"] is None:
+        w["seq"] = w["seq_per_gpu"] * P
+    B, H, kvH, S, D = w["batch"], w["heads"], w["kv_heads"], w["seq"], w["head_dim"]
+    layout = LAYOUTS[w["layout"]]
+    doc_len = S // 4 if w["doc_len"] == "seq/4" else int(w["doc_len"])
+    w["doc_len"] = doc_len
+    part = api.RingPartition(P, rank, S, layout, w["n_splits"])
     rows = part.local_positions()
     sloc = len(rows)
 
-    # Synthetic N(0,1) inputs, one seeded generator for the global tensors; each rank keeps its rows.
-    g = torch.Generator(device="cpu").manual_seed(42)
-    host = [torch.randn((B, H, S, D), generator=g).to(torch.float16)[:, :, rows].contiguous().pin_memory()
-            for _ in range(3)]
-    dq, dk, dv = (t.to(dev, non_blocking=True) for t in host)
+    if args.workload == "config2":
+        # Synthetic N(0,1) inputs, one seeded generator for the global tensors; each rank keeps its rows.
+        g = torch.Generator(device="cpu").manual_seed(42)
+        host = [torch.randn((B, H, S, D), generator=g).to(torch.float16)[:, :, rows].contiguous().pin_memory()
+                for _ in range(3)]
+        dq, dk, dv = (t.to(dev, non_blocking=True) for t in host)
+    else:
+        # The larger workloads generate each rank's shard on its GPU (same distribution, seed + rank);
+        # materialising the global tensors on the host would take tens of GB.
+        g = torch.Generator(device=dev).manual_seed(42 + rank)
+        dq = (torch.randn((B, H, sloc, D), generator=g, device=dev) * w["scale"]).to(torch.float16)
+        dk = (torch.randn((B, kvH, sloc, D), generator=g, device=dev) * w["scale"]).to(torch.float16)
+        dv = (torch.randn((B, kvH, sloc, D), generator=g, device=dev) * w["scale"]).to(torch.float16)
+        host = [t.cpu().pin_memory() for t in (dq, dk, dv)]
     out = torch.empty((B, H, sloc, D), dtype=torch.float32, device=dev)
     host_out = torch.empty((B, H, sloc, D), dtype=torch.float32).pin_memory()
     ring = api.Ring(rank, P)
@@ -218,18 +248,21 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
 
     def one_pass():
-        ring.prefill(dq, dk, dv, seq=S, causal=True, layout=1, n_splits=w["n_splits"], out=out)
+        ring.prefill(dq, dk, dv, seq=S, causal=True, layout=layout, n_splits=w["n_splits"], doc_len=doc_len,
+                     out=out)
 
     qmap1 = kmap1 = None
+    stride1 = 1
     if P == 1:
-        qmap1, kmap1, _ = part.step_maps(0)
+        qmap1, kmap1, stride1 = part.step_maps(0)
 
     def one_pass_host():
         if P == 1:
             # the host-buffer entry point of the C ABI: upload, step, download, synchronise
             api.check(api.lib().ra_prefill_host(
                 api.RA_F16, host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), host_out.data_ptr(),
-                None, api.AttentionShape(B, H, S, S, D).c(), qmap1, kmap1, 1, api.RA_STEP_CAUSAL, 0))
+                None, api.AttentionShape(B, H, S, S, D, kvH).c(), qmap1, kmap1, stride1, api.RA_STEP_CAUSAL,
+                doc_len))
         else:
             dq.copy_(host[0], non_blocking=True)
             dk.copy_(host[1], non_blocking=True)
@@ -277,8 +310,10 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
 
-    flops = causal_flops(B, H, S, D)
+    # causal-adjusted FLOPs; with documents the mask is block-diagonal causal (per document)
+    flops = causal_flops(B, H, S, D) if not doc_len else (S // doc_len) * causal_flops(B, H, doc_len, D)
     peaks = measured_peaks()
+    checked = check_rows(api, torch, dist, w, rank, P, rows, dq, dk, dv, out, dev) if args.check_rows else None
     line = None
     if rank == 0:
         value = flops / (ms * 1e-3) / 1e12
@@ -289,21 +324,23 @@ def run_gpu_arm(args):
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": P, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
-            "config": {"workload": "causal zig-zag ring-overlap prefill fp16 B1 S32768 H8 D64 (config 2)", **w,
+            "config": {"workload": w["name"], **{k: v for k, v in w.items() if k not in ("name", "seq_per_gpu")},
                        "cp_size": P, "per_gpu_tflops": per_gpu, "l2": "256 MB flush between timed iterations",
                        "timing": "CUDA events per pass on the launching stream, mean of K, max over ranks"},
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "ra_prefill_host" if P == 1 else "pinned H2D + ra_ring_prefill + D2H per rank"},
-            "gpu_launches": K * P,  # one step kernel per ring step per pass on each rank
+            "gpu_launches": K * P * P,  # one step kernel per ring step per pass on each of the P ranks
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": per_gpu / peaks["tflops"], "traffic": None,
                          "peak_source": f"{peaks['source']} bf16 GEMM burst",
-                         "kernel": "step_tc_kernel<64> (one launch per ring step)"},
+                         "kernel": f"step_tc_kernel<{D}> (one launch per ring step)"},
             "device_status": status,
         }
-    if P == 1 and rank == 0:
+        if checked is not None:
+            line["checked_rows"] = checked
+    if P == 1 and rank == 0 and args.workload == "config2":
         if not args.no_decode:
             line["decode"] = bench_decode(api, torch, dev, args, peaks)
         if not args.no_cpu:
@@ -317,6 +354,42 @@ def run_gpu_arm(args):
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def check_rows(api, torch, dist, w, rank, P, rows, dq, dk, dv, out, dev):
+    """Parity at full size: a few output rows of head 0 on every rank against the CPU oracle
+    (one causal row over the keys of its own document). K/V of head 0 are gathered from all
+    ranks for this; nothing here is timed."""
+    import numpy as np
+
+    import oracle
+    S, D, doc = w["seq"], w["head_dim"], w["doc_len"]
+    kh, vh, pos = dk[0, 0].contiguous(), dv[0, 0].contiguous(), rows.to(dev)
+    if P > 1:
+        ks = [torch.empty_like(kh) for _ in range(P)]
+        vs = [torch.empty_like(vh) for _ in range(P)]
+        ps = [torch.empty_like(pos) for _ in range(P)]
+        dist.all_gather(ks, kh)
+        dist.all_gather(vs, vh)
+        dist.all_gather(ps, pos)
+        kh, vh, pos = torch.cat(ks), torch.cat(vs), torch.cat(ps)
+    order = torch.argsort(pos)
+    kg = kh[order].float().cpu().numpy()  # keys of head 0 in global order
+    vg = vh[order].float().cpu().numpy()
+    worst, n = 0.0, 0
+    local = [0, 1, len(rows) // 4 - 1, len(rows) // 4, len(rows) // 2 + 5, len(rows) - 1]
+    for li in local:
+        p = int(rows[li])
+        lo = (p // doc) * doc if doc else 0
+        want, _ = oracle.attention_row(dq[0, 0, li].float().cpu().numpy(), kg[lo:p + 1], vg[lo:p + 1])
+        got = out[0, 0, li].cpu().numpy()
+        err = np.abs(got - want)
+        assert np.all(err <= 1e-3 + 1e-3 * np.abs(want)), f"rank {rank} row {p}: max err {err.max()}"
+        worst, n = max(worst, float(err.max())), n + 1
+    t = torch.tensor([worst], device=dev)
+    if P > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"rows_per_rank": n, "max_abs_err": float(t[0]), "tolerance": "atol=rtol=1e-3 vs CPU oracle"}
 
 
 def bench_decode(api, torch, dev, args, peaks):
@@ -412,6 +485,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS),
+                    help="prefill workload; config2 is the benchmark line, the others are for the tables")
+    ap.add_argument("--check-rows", action="store_true",
+                    help="also check a few output rows per rank against the CPU oracle (untimed)")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -194,11 +194,13 @@ int ra_prefill_host(int dtype, const void* q_host, const void* k_host, const voi
   const size_t kn = static_cast<size_t>(s->batch) * kvH * s->seq_k * s->head_dim;
   // Per-thread device buffers that grow on demand and are reused across calls, so a
   // benchmark loop measures copies and kernels, not cudaMalloc.
+  constexpr int kHostPipeEvents = 16;
   struct Scratch {
     void* p = nullptr;
     size_t bytes = 0;
     int dev = -1;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr, s_in = nullptr, s_out = nullptr;
+    cudaEvent_t e_in[kHostPipeEvents], e_done[kHostPipeEvents];
   };
   thread_local Scratch sc;
   int dev = 0;
@@ -231,20 +233,84 @@ int ra_prefill_host(int dtype, const void* q_host, const void* k_host, const voi
   base += (rows * 4 + a256) & ~a256;
   float* dlse = reinterpret_cast<float*>(base);
   cudaStream_t st = sc.stream;
-  RAB_CUDA(cudaMemcpyAsync(dq, q_host, qn * es, cudaMemcpyHostToDevice, st));
-  RAB_CUDA(cudaMemcpyAsync(dk, k_host, kn * es, cudaMemcpyHostToDevice, st));
-  RAB_CUDA(cudaMemcpyAsync(dv, v_host, kn * es, cudaMemcpyHostToDevice, st));
   const unsigned f = (flags & (RA_STEP_CAUSAL | RA_STEP_FORCE_SIMT)) | RA_STEP_FRESH |
                      RA_STEP_FINALIZE;
-  int rc = step_ex(dtype, dq, dk, dv, dout, dm, dl, *s, make_posmap(*qmap), make_posmap(*kmap),
-                   pos_stride > 0 ? pos_stride : 1, f, doc_len, 0, st);
-  if (rc != RA_OK) return rc;
-  RAB_CUDA(cudaMemcpyAsync(out_host, dout, qn * 4, cudaMemcpyDeviceToHost, st));
-  if (lse_host) {
-    rc = ra_attention_lse(dm, dl, dlse, rows, st);
-    if (rc != RA_OK) return rc;
-    RAB_CUDA(cudaMemcpyAsync(lse_host, dlse, rows * 4, cudaMemcpyDeviceToHost, st));
+  const PosMap qm = make_posmap(*qmap), km = make_posmap(*kmap);
+  const int stride = pos_stride > 0 ? pos_stride : 1;
+
+  // With one KV head per query head the (batch, head) slices are independent and contiguous,
+  // so the pass is pipelined over groups of them: upload of group c+1, kernel of group c and
+  // download of group c-1 run on three streams, which hides most of the PCIe time behind
+  // the other direction and the kernel. Groups are sized to keep the kernel's grid at about
+  // two waves of the SM count.
+  const int bh_total = s->batch * s->heads;
+  int groups = 1, bh_per_group = bh_total;
+  if (kvH == s->heads && bh_total >= 2 && s->seq_q > 0) {
+    const int qblocks = (s->seq_q + 255) / 256;
+    bh_per_group = std::max(1, (2 * 148 + qblocks - 1) / qblocks);
+    groups = (bh_total + bh_per_group - 1) / bh_per_group;
+    if (groups > kHostPipeEvents) {
+      bh_per_group = (bh_total + kHostPipeEvents - 1) / kHostPipeEvents;
+      groups = (bh_total + bh_per_group - 1) / bh_per_group;
+    }
   }
+  if (groups < 2) {
+    RAB_CUDA(cudaMemcpyAsync(dq, q_host, qn * es, cudaMemcpyHostToDevice, st));
+    RAB_CUDA(cudaMemcpyAsync(dk, k_host, kn * es, cudaMemcpyHostToDevice, st));
+    RAB_CUDA(cudaMemcpyAsync(dv, v_host, kn * es, cudaMemcpyHostToDevice, st));
+    int rc = step_ex(dtype, dq, dk, dv, dout, dm, dl, *s, qm, km, stride, f, doc_len, 0, st);
+    if (rc != RA_OK) return rc;
+    RAB_CUDA(cudaMemcpyAsync(out_host, dout, qn * 4, cudaMemcpyDeviceToHost, st));
+    if (lse_host) {
+      rc = ra_attention_lse(dm, dl, dlse, rows, st);
+      if (rc != RA_OK) return rc;
+      RAB_CUDA(cudaMemcpyAsync(lse_host, dlse, rows * 4, cudaMemcpyDeviceToHost, st));
+    }
+    RAB_CUDA(cudaStreamSynchronize(st));
+    return RA_OK;
+  }
+  if (sc.s_in == nullptr) {
+    RAB_CUDA(cudaStreamCreateWithFlags(&sc.s_in, cudaStreamNonBlocking));
+    RAB_CUDA(cudaStreamCreateWithFlags(&sc.s_out, cudaStreamNonBlocking));
+    for (int i = 0; i < kHostPipeEvents; ++i) {
+      RAB_CUDA(cudaEventCreateWithFlags(&sc.e_in[i], cudaEventDisableTiming));
+      RAB_CUDA(cudaEventCreateWithFlags(&sc.e_done[i], cudaEventDisableTiming));
+    }
+  }
+  const size_t q_head = static_cast<size_t>(s->seq_q) * s->head_dim;  // elements per (b,h)
+  const size_t k_head = static_cast<size_t>(s->seq_k) * s->head_dim;
+  for (int g = 0; g < groups; ++g) {
+    const int bh0 = g * bh_per_group;
+    const int nbh = std::min(bh_per_group, bh_total - bh0);
+    const size_t qo = bh0 * q_head, ko = bh0 * k_head, ro = static_cast<size_t>(bh0) * s->seq_q;
+    unsigned char* gq = static_cast<unsigned char*>(dq) + qo * es;
+    unsigned char* gk = static_cast<unsigned char*>(dk) + ko * es;
+    unsigned char* gv = static_cast<unsigned char*>(dv) + ko * es;
+    RAB_CUDA(cudaMemcpyAsync(gq, static_cast<const unsigned char*>(q_host) + qo * es,
+                             nbh * q_head * es, cudaMemcpyHostToDevice, sc.s_in));
+    RAB_CUDA(cudaMemcpyAsync(gk, static_cast<const unsigned char*>(k_host) + ko * es,
+                             nbh * k_head * es, cudaMemcpyHostToDevice, sc.s_in));
+    RAB_CUDA(cudaMemcpyAsync(gv, static_cast<const unsigned char*>(v_host) + ko * es,
+                             nbh * k_head * es, cudaMemcpyHostToDevice, sc.s_in));
+    RAB_CUDA(cudaEventRecord(sc.e_in[g], sc.s_in));
+    RAB_CUDA(cudaStreamWaitEvent(st, sc.e_in[g], 0));
+    ra_shape gs{1, nbh, s->seq_q, s->seq_k, s->head_dim, nbh};
+    int rc = step_ex(dtype, gq, gk, gv, dout + qo, dm + ro, dl + ro, gs, qm, km, stride, f,
+                     doc_len, 0, st);
+    if (rc != RA_OK) return rc;
+    if (lse_host) {
+      rc = ra_attention_lse(dm + ro, dl + ro, dlse + ro, static_cast<size_t>(nbh) * s->seq_q, st);
+      if (rc != RA_OK) return rc;
+    }
+    RAB_CUDA(cudaEventRecord(sc.e_done[g], st));
+    RAB_CUDA(cudaStreamWaitEvent(sc.s_out, sc.e_done[g], 0));
+    RAB_CUDA(cudaMemcpyAsync(out_host + qo, dout + qo, nbh * q_head * 4, cudaMemcpyDeviceToHost,
+                             sc.s_out));
+    if (lse_host)
+      RAB_CUDA(cudaMemcpyAsync(lse_host + ro, dlse + ro, static_cast<size_t>(nbh) * s->seq_q * 4,
+                               cudaMemcpyDeviceToHost, sc.s_out));
+  }
+  RAB_CUDA(cudaStreamSynchronize(sc.s_out));
   RAB_CUDA(cudaStreamSynchronize(st));
   return RA_OK;
 }

@@ -117,3 +117,21 @@ def test_decode_full_size_cache_linearity_and_sampled_heads():
     # linear in V: attention(q, k, 2v) == 2 attention(q, k, v) (doubling is exact in fp16)
     out2 = run(v * 2)
     assert_close(out2.cpu().numpy(), 2 * out.cpu().numpy(), 1e-6, 1e-6, "linearity")
+
+
+def test_host_buffer_prefill_pipelined_equals_device_resident_result():
+    # the benchmark shape through the host-buffer entry point (pipelined over head groups) must
+    # give exactly what the same kernel gives on device-resident tensors
+    B, H, S, D = 1, 8, 32768, 64
+    q, k, v = gen(11, (B, H, S, D)), gen(12, (B, H, S, D)), gen(13, (B, H, S, D))
+    shape = api.AttentionShape(B, H, S, S, D)
+    out = torch.empty((B, H, S, D), device="cuda")
+    m = torch.empty((B, H, S), device="cuda")
+    l = torch.empty((B, H, S), device="cuda")
+    one = SegMap.make([0], S)
+    api.attention_step_ex(q, k, v, out, m, l, shape, one, one, causal=True, fresh=True, finalize=True)
+    lse = api.attention_lse(m, l)
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    for _ in range(2):
+        h_out, h_lse = api.prefill_host(hq, hk, hv, shape, one, one, causal=True, want_lse=True)
+    assert torch.equal(h_out, out.cpu()) and torch.equal(h_lse, lse.cpu())
