@@ -292,6 +292,12 @@ def run_gpu_arm(args):
     barrier()
     ms_steps = [a.elapsed_time(b) for a, b in ev]
     ms = sum(ms_steps) / K
+    # one more pass with the driver's own event timings (the reference's RingResult fields):
+    # compute = sum of the step kernels, comm = sum of the send/recv groups on the side stream,
+    # wait = pass time the compute stream spent not computing (transfers that were not hidden)
+    _, ring_t = ring.prefill(dq, dk, dv, seq=S, causal=True, layout=layout, n_splits=w["n_splits"],
+                             doc_len=doc_len, out=out, timed=True)
+    ring_times = [ring_t.total_ms, ring_t.comp_ms, ring_t.comm_ms, ring_t.wait_ms]
 
     # end to end: host buffers in, host result out, copies inside the timed region
     for _ in range(2):
@@ -306,9 +312,10 @@ def run_gpu_arm(args):
     status = api.device_status()
 
     if world > 1:
-        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, ms_e2e] + ring_times, device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
+        ring_times = [float(x) for x in t[2:]]
 
     # causal-adjusted FLOPs; with documents the mask is block-diagonal causal (per document)
     flops = causal_flops(B, H, S, D) if not doc_len else (S // doc_len) * causal_flops(B, H, doc_len, D)
@@ -337,9 +344,16 @@ def run_gpu_arm(args):
                          "peak_source": f"{peaks['source']} bf16 GEMM burst",
                          "kernel": f"step_tc_kernel<{D}> (one launch per ring step)"},
             "device_status": status,
+            "ring": {"total_ms": ring_times[0], "comp_ms": ring_times[1], "comm_ms": ring_times[2],
+                     "wait_ms": ring_times[3], "exposed_comm_frac": ring_times[3] / max(ring_times[0], 1e-9),
+                     "note": "one pass, max over ranks; wait = pass time not covered by step kernels"},
         }
         if checked is not None:
             line["checked_rows"] = checked
+    if P > 1 and args.workload == "config2" and not args.no_decode:
+        dec = bench_ring_decode(api, torch, dist, dev, args, peaks, ring, rank, P)
+        if rank == 0:
+            line["decode"] = dec
     if P == 1 and rank == 0 and args.workload == "config2":
         if not args.no_decode:
             line["decode"] = bench_decode(api, torch, dev, args, peaks)
@@ -475,6 +489,55 @@ def run_profile_case(args):
     assert api.device_status()[0] == 0
     print(json.dumps({"profile_case": args.profile, "ok": True}))
     return 0
+
+
+def bench_ring_decode(api, torch, dist, dev, args, peaks, ring, rank, P):
+    """The decode workload with the cache sharded over P ranks (262144 / P cached tokens each):
+    every step appends on the round-robin owner, folds the local shard, all-gathers the
+    partials and merges (ra_ring_decode_step). tokens/s counts the batch rows per step."""
+    d = DECODE
+    B, H, kvH, D, L = d["batch"], d["heads"], d["kv_heads"], d["head_dim"], d["prompt"]
+    per = L // P
+    n = max(args.steps, 10)
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    cache = api.DeviceKVCache(B, kvH, per + n + 8, D, torch.float16)
+    k0 = torch.randn((B, kvH, per, D), generator=g, device=dev, dtype=torch.float16)
+    v0 = torch.randn((B, kvH, per, D), generator=g, device=dev, dtype=torch.float16)
+    cache.copy_prefill(k0, v0, per)
+    del k0, v0
+    gq = torch.Generator(device=dev).manual_seed(99)  # the query is replicated: same seed on every rank
+    q = torch.randn((B, H, 1, D), generator=gq, device=dev, dtype=torch.float16)
+    kn = torch.randn((B, kvH, 1, D), generator=g, device=dev, dtype=torch.float16)
+    vn = torch.randn((B, kvH, 1, D), generator=g, device=dev, dtype=torch.float16)
+    out = torch.empty((B, H, 1, D), device=dev)
+    lens = [per] * P
+    stream = torch.cuda.current_stream()
+    t = 0
+    for _ in range(3):
+        lens[t % P] += 1
+        ring.decode_step(q, kn, vn, t % P, cache, lens, out)
+        t += 1
+    torch.cuda.synchronize()
+    dist.barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+    for i in range(n):
+        lens[t % P] += 1
+        ev[i][0].record(stream)
+        ring.decode_step(q, kn, vn, t % P, cache, lens, out)
+        ev[i][1].record(stream)
+        t += 1
+    torch.cuda.synchronize()
+    ms = torch.tensor([sum(a.elapsed_time(b) for a, b in ev) / n], device=dev, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms[0])
+    kv_bytes = 2.0 * B * kvH * L * D * 2
+    gbs = kv_bytes / (ms * 1e-3) / 1e9
+    return {"workload": f"decode B4 H32 kvH8 D128 fp16, 262144 cached tokens sharded over {P} ranks (config 4)",
+            "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "hbm_gbs": gbs, "hbm_gbs_per_gpu": gbs / P,
+            "roofline": {"bound": "hbm", "achieved": gbs / P, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / P / peaks["hbm_gbs"], "traffic": None,
+                         "peak_source": f"{peaks['source']} copy bandwidth",
+                         "note": "per GPU, whole step including the all-gather of partials and the merge"}}
 
 
 def main():

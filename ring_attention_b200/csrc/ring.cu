@@ -113,7 +113,13 @@ static int ring_finish_create(int rank, int cp, ncclComm_t comm, bool own, ra_ri
   r->own_comm = own;
   r->dec_buf = nullptr;
   r->dec_bytes = 0;
-  RAB_CUDA(cudaStreamCreateWithFlags(&r->comm_stream, cudaStreamNonBlocking));
+  // The transfer stream gets the highest priority: the step kernel keeps every SM full (one
+  // block per SM, all registers), so the few blocks of a send/recv kernel can only run on SMs
+  // the block scheduler hands them first. Without the priority they queue behind the step
+  // kernel's blocks and the "overlapped" transfer runs after the compute it should hide under.
+  int prio_lo = 0, prio_hi = 0;
+  RAB_CUDA(cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi));
+  RAB_CUDA(cudaStreamCreateWithPriority(&r->comm_stream, cudaStreamNonBlocking, prio_hi));
   RAB_CUDA(cudaEventCreate(&r->ev_start));
   RAB_CUDA(cudaEventCreate(&r->ev_end));
   for (int i = 0; i < kMaxRanks; ++i) {
