@@ -249,7 +249,7 @@ def run_gpu_arm(args):
 
     def one_pass():
         ring.prefill(dq, dk, dv, seq=S, causal=True, layout=layout, n_splits=w["n_splits"], doc_len=doc_len,
-                     out=out)
+                     out=out, schedule=args.schedule)
 
     qmap1 = kmap1 = None
     stride1 = 1
@@ -296,7 +296,7 @@ def run_gpu_arm(args):
     # compute = sum of the step kernels, comm = sum of the send/recv groups on the side stream,
     # wait = pass time the compute stream spent not computing (transfers that were not hidden)
     _, ring_t = ring.prefill(dq, dk, dv, seq=S, causal=True, layout=layout, n_splits=w["n_splits"],
-                             doc_len=doc_len, out=out, timed=True)
+                             doc_len=doc_len, out=out, timed=True, schedule=args.schedule)
     ring_times = [ring_t.total_ms, ring_t.comp_ms, ring_t.comm_ms, ring_t.wait_ms]
 
     # end to end: host buffers in, host result out, copies inside the timed region
@@ -346,6 +346,9 @@ def run_gpu_arm(args):
             "device_status": status,
             "ring": {"total_ms": ring_times[0], "comp_ms": ring_times[1], "comm_ms": ring_times[2],
                      "wait_ms": ring_times[3], "exposed_comm_frac": ring_times[3] / max(ring_times[0], 1e-9),
+                     "schedule": (args.schedule if args.schedule != "auto" else
+                                  ("gather" if dk.numel() * dk.element_size() <= (32 << 20) else "ring"))
+                     if P > 1 else None,
                      "note": "one pass, max over ranks; wait = pass time not covered by step kernels"},
         }
         if checked is not None:
@@ -552,6 +555,8 @@ def main():
                     help="prefill workload; config2 is the benchmark line, the others are for the tables")
     ap.add_argument("--check-rows", action="store_true",
                     help="also check a few output rows per rank against the CPU oracle (untimed)")
+    ap.add_argument("--schedule", default="auto", choices=["auto", "ring", "gather"],
+                    help="how K/V shards travel at N>1: hop-by-hop ring, one all-gather, or by shard size")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -124,6 +124,21 @@ RA_API int ra_attention_step_ex(int dtype, const void* q, const void* k, const v
                                 const ra_segmap* kmap, int pos_stride, unsigned flags,
                                 long long doc_len, int kv_row_stride, ra_stream stream);
 
+/* The general step over key segments that sit in n_shards stacked shards instead of one tensor:
+ * k / v point at shard 0, every shard is (batch * kv_heads, shard_rows, head_dim) and shard s
+ * starts s * batch * kv_heads * shard_rows * head_dim elements later (the receive buffer of an
+ * all-gather of per-rank shards). Key segment i of kmap is rows seg_row[i] .. seg_row[i] +
+ * seg_len of shard seg_shard[i]; shape->seq_k = kmap->n_seg * kmap->seg_len. 16-bit dtypes and
+ * head_dim 64 / 128 only (RA_ERR_INVALID otherwise). One launch then folds the shards of
+ * several ring steps; the reference has no counterpart (its all-gather mode copies the shards
+ * into one tensor first, src/ring_loop.cu:273-420). */
+RA_API int ra_attention_step_stacked(int dtype, const void* q, const void* k, const void* v,
+                                     float* out, float* m, float* l, const ra_shape* shape,
+                                     const ra_segmap* qmap, const ra_segmap* kmap,
+                                     const int* seg_shard, const int* seg_row, int n_shards,
+                                     int shard_rows, int pos_stride, unsigned flags,
+                                     long long doc_len, ra_stream stream);
+
 /* out_i *= 1 / l_i (0 where l_i <= 0). Replaces launch_attention_finalize
  * (src/attention.hpp:136, src/attention_step.cu:556-562). */
 RA_API int ra_attention_finalize(float* out, const float* l, const ra_shape* shape,
@@ -273,7 +288,16 @@ typedef struct ra_ring_config {
   int layout;    /* 0 contiguous, 1 zig-zag, 2 striped */
   int n_splits;  /* zig-zag sub-groups per rank (2 * zigzag_n) */
   long long doc_len; /* 0 = no document mask */
+  int schedule;      /* RA_SCHEDULE_*; 0 (auto) picks by shard size */
 } ra_ring_config;
+
+/* How the K/V shards reach every rank. RING is the reference's overlapped hop-by-hop rotation
+ * (RingMode::RingOverlap, src/ring_loop.hpp:16); GATHER is one all-gather overlapped with the
+ * step on the rank's own shard, then the remaining steps back to back (what the reference's
+ * RingMode::AllGather does, src/ring_loop.cu:273-420, but still one masked step per source
+ * shard). AUTO takes GATHER while a shard tensor is at most 32 MiB, where a hop's latency
+ * cannot hide under a step, and RING above. Results are identical. */
+enum { RA_SCHEDULE_AUTO = 0, RA_SCHEDULE_RING = 1, RA_SCHEDULE_GATHER = 2 };
 
 /* Mirrors RingResult (src/ring_loop.hpp:30-36); times of this rank, milliseconds. */
 typedef struct ra_ring_result {

@@ -45,7 +45,8 @@ class RingConfig(C.Structure):
     """ra_ring_config: the ring-overlap part of RingConfig (reference src/ring_loop.hpp:38-62)."""
     _fields_ = [("batch", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("seq", C.c_int),
                 ("head_dim", C.c_int), ("dtype", C.c_int), ("causal", C.c_int),
-                ("layout", C.c_int), ("n_splits", C.c_int), ("doc_len", C.c_longlong)]
+                ("layout", C.c_int), ("n_splits", C.c_int), ("doc_len", C.c_longlong),
+                ("schedule", C.c_int)]
 
 
 class RingResult(C.Structure):
@@ -75,6 +76,10 @@ _SIG = {
     "ra_attention_step_ex": (C.c_int, [C.c_int, _P, _P, _P, _P, _P, _P, C.POINTER(Shape),
                                        C.POINTER(SegMap), C.POINTER(SegMap), C.c_int, C.c_uint,
                                        C.c_longlong, C.c_int, _P]),
+    "ra_attention_step_stacked": (C.c_int, [C.c_int, _P, _P, _P, _P, _P, _P, C.POINTER(Shape),
+                                            C.POINTER(SegMap), C.POINTER(SegMap),
+                                            C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int,
+                                            C.c_int, C.c_int, C.c_uint, C.c_longlong, _P]),
     "ra_attention_finalize": (C.c_int, [_P, _P, C.POINTER(Shape), _P]),
     "ra_attention_lse": (C.c_int, [_P, _P, _P, C.c_size_t, _P]),
     "ra_float_to_half": (C.c_int, [_P, _P, C.c_size_t, _P]),

@@ -97,6 +97,21 @@ def attention_step_ex(q, k, v, out, m, l, shape, qmap, kmap, pos_stride=1, causa
                                      pos_stride, flags, doc_len, kv_row_stride, _stream()))
 
 
+def attention_step_stacked(q, k, v, out, m, l, shape, qmap, kmap, seg_shard, seg_row, *,
+                           pos_stride=1, causal=False, fresh=False, finalize=False, doc_len=0):
+    """General step whose key segments sit in stacked shards: ``k`` / ``v`` are
+    (n_shards, B, kvH, shard_rows, D); segment i is rows seg_row[i].. of shard seg_shard[i]."""
+    flags = ((RA_STEP_CAUSAL if causal else 0) | (RA_STEP_FRESH if fresh else 0) |
+             (RA_STEP_FINALIZE if finalize else 0))
+    n = len(seg_shard)
+    shard = (C.c_int * n)(*seg_shard)
+    row = (C.c_int * n)(*seg_row)
+    check(lib().ra_attention_step_stacked(_dtype(q), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(m),
+                                          _ptr(l), C.byref(shape.c()), C.byref(qmap),
+                                          C.byref(kmap), shard, row, k.shape[0], k.shape[3],
+                                          pos_stride, flags, doc_len, _stream()))
+
+
 def launch_attention_decode_step(q, k, v, out, m, l, shape, q_offset, k_offset, causal,
                                  kv_row_stride=0, workspace=None):
     """``launch_attention_decode_step`` (reference src/attention.hpp:128-131); any dtype."""
@@ -356,12 +371,14 @@ class Ring:
             pass
 
     def prefill(self, q, k, v, *, seq, causal, layout=0, n_splits=2, doc_len=0, want_lse=False,
-                timed=False, out=None):
+                timed=False, out=None, schedule="auto"):
         """One overlapped ring pass (``run_ring_attention`` in ring-overlap mode, reference
-        src/ring_loop_fp16.cu:522-818) over this rank's device shards."""
+        src/ring_loop_fp16.cu:522-818) over this rank's device shards. ``schedule`` is "ring"
+        (hop-by-hop rotation), "gather" (one all-gather, the reference's allgather mode) or
+        "auto" (by shard size)."""
         B, H, sloc, D = q.shape
         cfg = RingConfig(B, H, k.shape[1], seq, D, _dtype(q), int(causal), layout, n_splits,
-                         doc_len)
+                         doc_len, {"auto": 0, "ring": 1, "gather": 2}[schedule])
         need = lib().ra_ring_prefill_workspace_bytes(self._h, C.byref(cfg))
         if self._work is None or self._work.numel() < need:
             self._work = torch.empty(need, dtype=torch.uint8, device=q.device)

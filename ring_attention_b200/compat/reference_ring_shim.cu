@@ -8,9 +8,10 @@
 // total_ms = wall / iters, comm / comp / wait from device events, all MAX-reduced to rank 0,
 // --verify against cpu_attention on every rank's own rows (max absolute error, -1 where not
 // verified), the flag validation and its messages, and abort-on-error.
-// What differs, on purpose: every --mode runs the overlapped ring (on one NVSwitch box the
-// all-gather, blocking and 2-D schedules have nothing to offer; results are identical), a
-// ring step is one launch over the whole shard (so --segmented changes nothing), the
+// What differs, on purpose: --mode=allgather gathers the shards once and then runs one masked
+// step per source shard, every other --mode runs the overlapped ring or, for small shards, the
+// same gather (on one NVSwitch box the blocking and 2-D schedules have nothing to offer;
+// results are identical), a ring step is one launch over the whole shard (so --segmented changes nothing), the
 // communicator of nccl_init is wrapped, not rebuilt inside the timed region, and the initial
 // K/V shard is uploaded once, not once per pass (the ring never overwrites it).
 #include <cuda_fp16.h>
@@ -162,6 +163,7 @@ RingResult run_ring_attention(const RingConfig& cfg) {
   rc.layout = lay.mode;
   rc.n_splits = lay.n_splits;
   rc.doc_len = 0;
+  rc.schedule = cfg.mode == RingMode::AllGather ? RA_SCHEDULE_GATHER : RA_SCHEDULE_AUTO;
   const size_t work_bytes = ra_ring_prefill_workspace_bytes(ring, &rc);
   DeviceTensor<signed char> work(work_bytes);
 

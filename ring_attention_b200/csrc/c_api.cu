@@ -53,6 +53,13 @@ int step_ex(int dtype, const void* q, const void* k, const void* v, float* out, 
       static_cast<long long>(kv_row_stride > 0 ? kv_row_stride : s.seq_k) * s.head_dim;
   a.qmap = qmap;
   a.kmap = kmap;
+  for (int i = 0; i < RA_MAX_SEG; ++i) {
+    a.kseg_head[i] = 0;
+    a.kseg_row[i] = i * kmap.seg_len;
+  }
+  a.k_heads_total = static_cast<long long>(a.B) * a.kvH;
+  a.k_rows = s.seq_k;
+  a.k_stacked = false;
   a.stride = pos_stride;
   a.flags = flags;
   a.doc_len = doc_len;
@@ -68,6 +75,66 @@ int step_ex(int dtype, const void* q, const void* k, const void* v, float* out, 
     return launch_step_tc(dtype, a, stream);
   return launch_step_simt(dtype, a, stream);
 }
+
+}  // namespace
+
+bool step_stacked_supported(int dtype, int head_dim) {
+  return (dtype == RA_F16 || dtype == RA_BF16) && (head_dim == 64 || head_dim == 128);
+}
+
+int step_stacked(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
+                 float* l, const ra_shape& s, const PosMap& qmap, const PosMap& kmap,
+                 const int* seg_shard, const int* seg_row, int n_shards, int shard_rows,
+                 int pos_stride, unsigned flags, long long doc_len, cudaStream_t stream) {
+  RAB_REQUIRE(q && k && v && out && m && l && seg_shard && seg_row, RA_ERR_INVALID,
+              "stacked step: null argument");
+  RAB_REQUIRE(step_stacked_supported(dtype, s.head_dim), RA_ERR_INVALID,
+              "stacked step: needs a 16-bit dtype and head_dim 64 or 128");
+  RAB_REQUIRE(kmap.n_seg >= 1 && kmap.n_seg <= RA_MAX_SEG && kmap.seg_len >= 1 &&
+                  kmap.n_seg * kmap.seg_len == s.seq_k && n_shards >= 1 && shard_rows >= 1,
+              RA_ERR_INVALID, "stacked step: bad key map");
+  RAB_REQUIRE(qmap.n_seg >= 1 && qmap.n_seg <= RA_MAX_SEG && qmap.n_seg * qmap.seg_len == s.seq_q,
+              RA_ERR_INVALID, "stacked step: bad query map");
+  StepArgs a;
+  a.q = q;
+  a.k = k;
+  a.v = v;
+  a.out = out;
+  a.m = m;
+  a.l = l;
+  a.B = s.batch;
+  a.H = s.heads;
+  a.kvH = kv_heads_of(s);
+  a.Sq = s.seq_q;
+  a.Sk = s.seq_k;
+  a.D = s.head_dim;
+  a.kv_head_stride = static_cast<long long>(shard_rows) * s.head_dim;
+  a.qmap = qmap;
+  a.kmap = kmap;
+  const int heads_per_shard = a.B * a.kvH;
+  for (int i = 0; i < RA_MAX_SEG; ++i) {
+    a.kseg_head[i] = 0;
+    a.kseg_row[i] = 0;
+    if (i >= kmap.n_seg) continue;
+    RAB_REQUIRE(seg_shard[i] >= 0 && seg_shard[i] < n_shards && seg_row[i] >= 0 &&
+                    seg_row[i] + kmap.seg_len <= shard_rows,
+                RA_ERR_INVALID, "stacked step: segment %d outside its shard", i);
+    a.kseg_head[i] = seg_shard[i] * heads_per_shard;
+    a.kseg_row[i] = seg_row[i];
+  }
+  a.k_heads_total = static_cast<long long>(n_shards) * heads_per_shard;
+  a.k_rows = shard_rows;
+  a.k_stacked = true;
+  a.stride = pos_stride;
+  a.flags = flags;
+  a.doc_len = doc_len;
+  a.status = device_status_ptr();
+  RAB_REQUIRE(step_tc_supported(dtype, a), RA_ERR_INVALID,
+              "stacked step: the tensor-core kernel cannot take these arguments");
+  return launch_step_tc(dtype, a, stream);
+}
+
+namespace {
 
 int affine_step(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
                 float* l, const ra_shape* shape, int q_offset, int k_offset, int causal,
@@ -125,6 +192,24 @@ int ra_attention_step_ex(int dtype, const void* q, const void* k, const void* v,
   RAB_REQUIRE(doc_len >= 0, RA_ERR_INVALID, "attention step: doc_len must be >= 0");
   return step_ex(dtype, q, k, v, out, m, l, *shape, make_posmap(*qmap), make_posmap(*kmap),
                  pos_stride, flags, doc_len, kv_row_stride, static_cast<cudaStream_t>(stream));
+}
+
+int ra_attention_step_stacked(int dtype, const void* q, const void* k, const void* v, float* out,
+                              float* m, float* l, const ra_shape* shape, const ra_segmap* qmap,
+                              const ra_segmap* kmap, const int* seg_shard, const int* seg_row,
+                              int n_shards, int shard_rows, int pos_stride, unsigned flags,
+                              long long doc_len, ra_stream stream) {
+  RAB_REQUIRE(shape && qmap && kmap, RA_ERR_INVALID, "stacked step: null argument");
+  RAB_REQUIRE(doc_len >= 0 && pos_stride >= 1, RA_ERR_INVALID,
+              "stacked step: doc_len must be >= 0 and pos_stride >= 1");
+  RAB_REQUIRE(shape->batch > 0 && shape->heads > 0 && shape->seq_q > 0 && shape->seq_k > 0,
+              RA_ERR_INVALID, "stacked step: bad shape");
+  RAB_REQUIRE(qmap->n_seg >= 1 && qmap->n_seg <= RA_MAX_SEG && kmap->n_seg >= 1 &&
+                  kmap->n_seg <= RA_MAX_SEG,
+              RA_ERR_INVALID, "stacked step: segment count out of range");
+  return step_stacked(dtype, q, k, v, out, m, l, *shape, make_posmap(*qmap), make_posmap(*kmap),
+                      seg_shard, seg_row, n_shards, shard_rows, pos_stride, flags, doc_len,
+                      static_cast<cudaStream_t>(stream));
 }
 
 // Test hook: 1 = keep P in tensor memory (default), 0 = stage P through shared memory.

@@ -87,6 +87,15 @@ struct StepArgs {
   float* l;
   int B, H, kvH, Sq, Sk, D;
   long long kv_head_stride;  // elements between consecutive KV heads (rows * D)
+  // Where key segment i sits in the K / V allocation, seen as (k_heads_total, k_rows, D): head
+  // coordinate kseg_head[i] + (b * kvH + kv head), first row kseg_row[i]. One tensor with the
+  // segments concatenated along the sequence is kseg_head = 0, kseg_row[i] = i * seg_len; a
+  // stack of gathered shards puts every shard's heads after the previous shard's.
+  int kseg_head[RA_MAX_SEG];
+  int kseg_row[RA_MAX_SEG];
+  long long k_heads_total;
+  int k_rows;
+  bool k_stacked;  // true when the segment placement is not the concatenated default
   PosMap qmap, kmap;
   int stride;
   unsigned flags;
@@ -97,6 +106,16 @@ struct StepArgs {
 int launch_step_simt(int dtype, const StepArgs& a, cudaStream_t stream);
 int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream);
 bool step_tc_supported(int dtype, const StepArgs& a);
+
+// One step over key segments that live in several stacked shards (see StepArgs::kseg_head):
+// k / v point at shard 0, every shard is (B * kvH, shard_rows, D) and shard s starts
+// s * B * kvH heads later. kmap has one entry per key segment; seg_shard[i] and seg_row[i] place
+// it. Only the tensor-core kernel reads this layout: returns RA_ERR_INVALID where it cannot run.
+int step_stacked(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
+                 float* l, const ra_shape& shape, const PosMap& qmap, const PosMap& kmap,
+                 const int* seg_shard, const int* seg_row, int n_shards, int shard_rows,
+                 int pos_stride, unsigned flags, long long doc_len, cudaStream_t stream);
+bool step_stacked_supported(int dtype, int head_dim);
 
 // seq_q == 1 split-K decode step (decode.cu); workspace NULL = per-device buffer.
 int decode_step(int dtype, const void* q, const void* k, const void* v, float* out, float* m,

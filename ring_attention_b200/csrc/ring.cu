@@ -10,6 +10,9 @@
 // stream, double-buffered in local HBM, with an event fence so a buffer is not overwritten
 // while the previous step still reads it (src/ring_loop_fp16.cu:658-701).
 //
+// Small shards take a second schedule (see use_gather below): one all-gather instead of P-1
+// latency-bound hops.
+//
 // Decode replaces run_ring_decode_step (src/ring_decode.cu:85-226): the local partial is
 // computed straight into the all-gather send buffer (no pack copies), one ncclAllGather of
 // B*H*(D+2) floats per rank, then merge + normalise in one kernel.
@@ -206,14 +209,34 @@ static int check_cfg(const ra_ring* r, const ra_ring_config* c) {
   return RA_OK;
 }
 
+// Which schedule a pass uses. The hop-by-hop ring costs P-1 dependent NCCL exchanges; with
+// small shards each exchange is latency-bound (well over 100 us on NVSwitch whatever the size)
+// and cannot hide under a step kernel of a few tens of microseconds. One all-gather costs a
+// single such latency, so below kGatherMaxBytes per shard tensor the pass gathers every shard
+// once (overlapped with the step on the rank's own shard) and runs the other P-1 steps back to
+// back. Large shards keep the ring: its transfers hide completely and its workspace does not
+// grow with P.
+constexpr size_t kGatherMaxBytes = static_cast<size_t>(32) << 20;
+
+static bool use_gather(const ra_ring* r, const ra_ring_config* c, size_t kv_raw) {
+  if (r->cp <= 1) return false;
+  if (c->schedule == RA_SCHEDULE_RING) return false;
+  if (c->schedule == RA_SCHEDULE_GATHER) return true;
+  return kv_raw <= kGatherMaxBytes;
+}
+
 size_t ra_ring_prefill_workspace_bytes(const ra_ring* r, const ra_ring_config* c) {
   if (!r || !c || r->cp <= 0) return 0;
   const int kvH = c->kv_heads > 0 ? c->kv_heads : c->heads;
   const size_t es = c->dtype == RA_F32 ? 4 : 2;
   const size_t sloc = static_cast<size_t>(c->seq / r->cp);
-  const size_t kv_bytes = align256(static_cast<size_t>(c->batch) * kvH * sloc * c->head_dim * es);
+  const size_t kv_raw = static_cast<size_t>(c->batch) * kvH * sloc * c->head_dim * es;
+  const size_t kv_bytes = align256(kv_raw);
   const size_t ml = align256(static_cast<size_t>(c->batch) * c->heads * sloc * sizeof(float));
-  return (r->cp > 1 ? 4 * kv_bytes : 0) + 2 * ml + 256;
+  size_t kv = 0;
+  if (r->cp > 1)
+    kv = use_gather(r, c, kv_raw) ? 2 * align256(static_cast<size_t>(r->cp) * kv_raw) : 4 * kv_bytes;
+  return kv + 2 * ml + 256;
 }
 
 int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const void* k,
@@ -234,9 +257,14 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
   const size_t rows = static_cast<size_t>(c->batch) * c->heads * sloc;
   unsigned char* base = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(kv_work) + 255) & ~static_cast<uintptr_t>(255));
+  const bool gather = use_gather(r, c, kv_raw);
   unsigned char* buf_k[2] = {nullptr, nullptr};
   unsigned char* buf_v[2] = {nullptr, nullptr};
-  if (P > 1) {
+  if (P > 1 && gather) {
+    buf_k[0] = base;  // every rank's K shard, rank-major
+    buf_v[0] = base + align256(static_cast<size_t>(P) * kv_raw);
+    base += 2 * align256(static_cast<size_t>(P) * kv_raw);
+  } else if (P > 1) {
     buf_k[0] = base;
     buf_v[0] = base + kv_bytes;
     buf_k[1] = base + 2 * kv_bytes;
@@ -251,7 +279,75 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
 
   RAB_CUDA(cudaEventRecord(r->ev_start, stream));
   RAB_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_start, 0));
-  for (int s = 0; s < P; ++s) {
+  if (gather) {
+    RAB_CUDA(cudaEventRecord(r->ev_comm_begin[0], r->comm_stream));
+    RAB_NCCL(g_nccl.GroupStart());
+    RAB_NCCL(g_nccl.AllGather(k, buf_k[0], kv_raw, kNcclInt8, r->comm, r->comm_stream));
+    RAB_NCCL(g_nccl.AllGather(v, buf_v[0], kv_raw, kNcclInt8, r->comm, r->comm_stream));
+    RAB_NCCL(g_nccl.GroupEnd());
+    RAB_CUDA(cudaEventRecord(r->ev_comm[0], r->comm_stream));
+  }
+  int n_launch = 0;  // step kernels of this pass, for the event timings
+  if (gather) {
+    // step 0 on the rank's own shard while the all-gather runs
+    ra_segmap qmap, kmap;
+    int stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, 0, &qmap, &kmap);
+    RAB_REQUIRE(stride >= 1, RA_ERR_INVALID, "ring prefill: bad partition");
+    const unsigned causal_flag = c->causal ? RA_STEP_CAUSAL : 0u;
+    RAB_CUDA(cudaEventRecord(r->ev_comp_begin[0], stream));
+    rc = ra_attention_step_ex(c->dtype, q, k, v, out, m, l, &shape, &qmap, &kmap, stride,
+                              causal_flag | RA_STEP_FRESH, c->doc_len, 0, stream);
+    if (rc != RA_OK) return rc;
+    RAB_CUDA(cudaEventRecord(r->ev_comp[0], stream));
+    n_launch = 1;
+    RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[0], 0));
+    // The other P-1 shards, as many per launch as the segment table holds: one launch sees
+    // their key segments side by side, so a query block's loop runs over all of them and the
+    // launch has one tail instead of one per shard. Where the kernel that reads stacked
+    // shards does not apply (fp32, head_dim 32 / 256) every shard gets its own step.
+    const int nsg = kmap.n_seg;
+    const bool stacked = step_stacked_supported(c->dtype, c->head_dim);
+    const int per_launch = stacked ? (RA_MAX_SEG / nsg > 0 ? RA_MAX_SEG / nsg : 1) : 1;
+    for (int s0 = 1; s0 < P; s0 += per_launch) {
+      const int g = (P - s0 < per_launch) ? P - s0 : per_launch;
+      unsigned flags = causal_flag | (s0 + g == P ? RA_STEP_FINALIZE : 0u);
+      RAB_REQUIRE(n_launch < kMaxRanks, RA_ERR_INVALID, "ring prefill: too many launches");
+      RAB_CUDA(cudaEventRecord(r->ev_comp_begin[n_launch], stream));
+      if (stacked) {
+        PosMap km;
+        std::memset(&km, 0, sizeof(km));
+        km.n_seg = g * nsg;
+        km.seg_len = kmap.seg_len;
+        int seg_shard[RA_MAX_SEG], seg_row[RA_MAX_SEG];
+        for (int t = 0; t < g; ++t) {
+          ra_segmap kq, ks;
+          stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s0 + t, &kq, &ks);
+          RAB_REQUIRE(stride >= 1 && ks.n_seg == nsg && ks.seg_len == kmap.seg_len, RA_ERR_INVALID,
+                      "ring prefill: bad partition");
+          for (int i = 0; i < nsg; ++i) {
+            km.base[t * nsg + i] = ks.base[i];
+            seg_shard[t * nsg + i] = (r->rank - (s0 + t) + P) % P;  // the shard s hops away
+            seg_row[t * nsg + i] = i * kmap.seg_len;
+          }
+        }
+        ra_shape sh = shape;
+        sh.seq_k = km.n_seg * km.seg_len;
+        rc = step_stacked(c->dtype, q, buf_k[0], buf_v[0], out, m, l, sh, make_posmap(qmap), km,
+                          seg_shard, seg_row, P, sloc, stride, flags, c->doc_len, stream);
+      } else {
+        const size_t src = static_cast<size_t>((r->rank - s0 + P) % P);
+        ra_segmap kq, ks;
+        stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s0, &kq, &ks);
+        RAB_REQUIRE(stride >= 1, RA_ERR_INVALID, "ring prefill: bad partition");
+        rc = ra_attention_step_ex(c->dtype, q, buf_k[0] + src * kv_raw, buf_v[0] + src * kv_raw, out,
+                                  m, l, &shape, &kq, &ks, stride, flags, c->doc_len, 0, stream);
+      }
+      if (rc != RA_OK) return rc;
+      RAB_CUDA(cudaEventRecord(r->ev_comp[n_launch], stream));
+      ++n_launch;
+    }
+  }
+  for (int s = 0; s < P && !gather; ++s) {
     const void* cur_k = s == 0 ? k : buf_k[(s - 1) & 1];
     const void* cur_v = s == 0 ? v : buf_v[(s - 1) & 1];
     if (s < P - 1) {
@@ -279,6 +375,7 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
                               flags, c->doc_len, 0, stream);
     if (rc != RA_OK) return rc;
     RAB_CUDA(cudaEventRecord(r->ev_comp[s], stream));
+    n_launch = s + 1;
   }
   if (lse) {
     rc = ra_attention_lse(m, l, lse, rows, stream);
@@ -290,13 +387,13 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
     RAB_CUDA(cudaStreamSynchronize(r->comm_stream));
     float ms = 0.f;
     double comp = 0.0, comm = 0.0;
-    for (int s = 0; s < P; ++s) {
+    for (int s = 0; s < n_launch; ++s) {
       RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_comp_begin[s], r->ev_comp[s]));
       comp += ms;
-      if (s < P - 1) {
-        RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_comm_begin[s], r->ev_comm[s]));
-        comm += ms;
-      }
+    }
+    for (int s = 0; s < (gather ? 1 : P - 1); ++s) {
+      RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_comm_begin[s], r->ev_comm[s]));
+      comm += ms;
     }
     RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_start, r->ev_end));
     result->total_ms = ms;

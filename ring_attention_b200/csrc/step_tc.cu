@@ -405,6 +405,8 @@ struct TcArgs {
   int H, kvH, Sq;
   int n_qblocks_per_seg;
   PosMap qmap, kmap;
+  int kseg_head[RA_MAX_SEG];  // key segment -> head-coordinate offset and first row in K / V
+  int kseg_row[RA_MAX_SEG];
   int stride;
   unsigned flags;
   long long doc_len;
@@ -518,7 +520,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int sk = 0; sk < a.kmap.n_seg && ok; ++sk) {
         const TileRange r = tile_range(a.kmap, sk, a.stride, causal, a.doc_len, qmin, qmax);
         for (int t = r.lo; t < r.hi && ok; ++t) {
-          const int k_row = sk * a.kmap.seg_len + t * kBN;
+          const int k_row = a.kseg_row[sk] + t * kBN;
+          const int k_head = a.kseg_head[sk] + kv_bh;
           for (int which = 0; which < 2 && ok; ++which, ++it) {
             const int slot = it % C::kStages;
             if (it >= C::kStages)
@@ -529,7 +532,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const CUtensorMap* map = which == 0 ? &tmap_k : &tmap_v;
             for (int bx = 0; bx < C::kBoxes; ++bx)
               tma_load_3d(s_kv + slot * C::kTileBytes + bx * (kBN * 128), map,
-                          bar_kv_full + 8 * slot, bx * 64, k_row, kv_bh);
+                          bar_kv_full + 8 * slot, bx * 64, k_row, k_head);
           }
         }
       }
@@ -972,9 +975,9 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   int rc = make_map(&mq, dtype, a.q, D, a.Sq, static_cast<long long>(a.B) * a.H,
                     static_cast<long long>(a.Sq) * D);
   if (rc != RA_OK) return rc;
-  rc = make_map(&mk, dtype, a.k, D, a.Sk, static_cast<long long>(a.B) * a.kvH, a.kv_head_stride);
+  rc = make_map(&mk, dtype, a.k, D, a.k_rows, a.k_heads_total, a.kv_head_stride);
   if (rc != RA_OK) return rc;
-  rc = make_map(&mv, dtype, a.v, D, a.Sk, static_cast<long long>(a.B) * a.kvH, a.kv_head_stride);
+  rc = make_map(&mv, dtype, a.v, D, a.k_rows, a.k_heads_total, a.kv_head_stride);
   if (rc != RA_OK) return rc;
 
   TcArgs t;
@@ -987,6 +990,10 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.n_qblocks_per_seg = (a.qmap.seg_len + kQBlock - 1) / kQBlock;
   t.qmap = a.qmap;
   t.kmap = a.kmap;
+  for (int i = 0; i < RA_MAX_SEG; ++i) {
+    t.kseg_head[i] = a.kseg_head[i];
+    t.kseg_row[i] = a.kseg_row[i];
+  }
   t.stride = a.stride;
   t.flags = a.flags;
   t.doc_len = a.doc_len;

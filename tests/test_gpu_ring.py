@@ -38,7 +38,8 @@ def _worker(rank, world, port, case, ret):
             for _ in range(2):  # twice: buffers and events are reused across passes
                 out, lse, res = ring.prefill(ql, kl, vl, seq=S, causal=case["causal"], layout=case["layout"],
                                              n_splits=case["n_splits"], doc_len=case.get("doc_len", 0),
-                                             want_lse=True, timed=True)
+                                             want_lse=True, timed=True,
+                                             schedule=case.get("schedule", "auto"))
             torch.cuda.synchronize()
             assert api.device_status()[0] == 0
             qf, kf, vf = (t.float().numpy() for t in (q, k, v))
@@ -112,19 +113,21 @@ def _world():
     return 4 if n >= 4 else 2
 
 
+@pytest.mark.parametrize("schedule", ["ring", "gather"])
 @pytest.mark.parametrize("layout,n_splits", [(1, 2), (0, 2), (2, 2), (1, 4)])
-def test_ring_prefill_fp16_causal(layout, n_splits):
+def test_ring_prefill_fp16_causal(layout, n_splits, schedule):
     world = _world()
     _run(world, dict(kind="prefill", B=1, H=4, kvH=2, S=world * n_splits * 256, D=64, causal=True,
-                     layout=layout, n_splits=n_splits))
+                     layout=layout, n_splits=n_splits, schedule=schedule))
 
 
 def test_ring_prefill_d128_noncausal_and_documents():
     world = _world()
     _run(world, dict(kind="prefill", B=2, H=4, kvH=4, S=world * 2 * 128, D=128, causal=False, layout=0, n_splits=2))
     S = world * 4 * 128
-    _run(world, dict(kind="prefill", B=1, H=2, kvH=2, S=S, D=128, causal=True, layout=1, n_splits=4,
-                     doc_len=S // 4))
+    for schedule in ("ring", "gather"):
+        _run(world, dict(kind="prefill", B=1, H=2, kvH=2, S=S, D=128, causal=True, layout=1, n_splits=4,
+                         doc_len=S // 4, schedule=schedule))
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16"])

@@ -336,3 +336,61 @@ def test_unsupported_head_dim_is_an_error_not_a_crash():
     with pytest.raises(api._lib.RingAttentionError) as e:
         api.launch_attention_step(q, q, q, out, m, l, api.AttentionShape(1, 1, 8, 8, 48), 0, 0, False)
     assert "unsupported head_dim=48" in str(e.value)
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.float16, 64), (torch.bfloat16, 128)])
+@pytest.mark.parametrize("layout,ns,chunk", [(1, 2, 48), (1, 4, 128), (2, 1, 200), (0, 1, 320)])
+def test_stacked_shards_fold_several_ring_steps_in_one_launch(dtype, D, layout, ns, chunk):
+    """The gather schedule on one GPU: every rank's K/V shard stacked as an all-gather leaves
+    them, step 0 on the rank's own shard, then ONE launch over the other P-1 shards."""
+    cp, rank, B, H, kvH = 4, 2, 1, 4, 2
+    sloc = ns * chunk if layout == 1 else chunk
+    S = cp * sloc
+    q, k, v = normal_inputs(11, B, H, kvH, S, S, D)
+    q, k, v = (round_to(x, dtype) for x in (q, k, v))
+    parts = [api.RingPartition(cp, r, S, layout, ns) for r in range(cp)]
+    rows = [p.local_positions().numpy() for p in parts]
+    dq = dev(q[:, :, rows[rank]], dtype)
+    ks = dev(np.stack([k[:, :, rows[r]] for r in range(cp)]), dtype)  # (cp, B, kvH, sloc, D)
+    vs = dev(np.stack([v[:, :, rows[r]] for r in range(cp)]), dtype)
+    out, m, l = state(B, H, sloc, D, poison=True)
+    shape = api.AttentionShape(B, H, sloc, sloc, D, kvH)
+    qmap, kmap0, stride = parts[rank].step_maps(0)
+    api.attention_step_ex(dq, ks[rank], vs[rank], out, m, l, shape, qmap, kmap0, stride, causal=True, fresh=True)
+    nsg = kmap0.n_seg
+    big = SegMap()
+    big.n_seg, big.seg_len = (cp - 1) * nsg, kmap0.seg_len
+    seg_shard, seg_row = [], []
+    for s in range(1, cp):
+        _, km, _ = parts[rank].step_maps(s)
+        for i in range(nsg):
+            big.base[(s - 1) * nsg + i] = km.base[i]
+            seg_shard.append((rank - s) % cp)
+            seg_row.append(i * km.seg_len)
+    shape_big = api.AttentionShape(B, H, sloc, (cp - 1) * sloc, D, kvH)
+    api.attention_step_stacked(dq, ks, vs, out, m, l, shape_big, qmap, big, seg_shard, seg_row,
+                               pos_stride=stride, causal=True, finalize=True)
+    torch.cuda.synchronize()
+    assert api.device_status()[0] == 0
+    want = oracle.cpu_attention(q, k, v, True, kv_heads=kvH)[:, :, rows[rank]]
+    tol = TOL[dtype]
+    assert_close(out.cpu().numpy(), want, tol, tol, "out")
+
+
+def test_stacked_step_rejects_what_the_tensor_core_kernel_cannot_read():
+    q = torch.zeros((1, 1, 64, 32), device="cuda", dtype=torch.float16)
+    ks = torch.zeros((2, 1, 1, 64, 32), device="cuda", dtype=torch.float16)
+    out, m, l = state(1, 1, 64, 32)
+    qm, km = SegMap(), SegMap()
+    qm.n_seg, qm.seg_len = 1, 64
+    km.n_seg, km.seg_len = 2, 64
+    with pytest.raises(RuntimeError):
+        api.attention_step_stacked(q, ks, ks, out, m, l, api.AttentionShape(1, 1, 64, 128, 32, 1), qm, km,
+                                   [0, 1], [0, 0])
+    q64 = torch.zeros((1, 1, 64, 64), device="cuda", dtype=torch.float16)
+    ks64 = torch.zeros((2, 1, 1, 64, 64), device="cuda", dtype=torch.float16)
+    out, m, l = state(1, 1, 64, 64)
+    with pytest.raises(RuntimeError):  # a segment that leaves its shard
+        api.attention_step_stacked(q64, ks64, ks64, out, m, l, api.AttentionShape(1, 1, 64, 128, 64, 1), qm, km,
+                                   [0, 1], [0, 32])
+    torch.cuda.synchronize()
