@@ -321,6 +321,14 @@ def run_gpu_arm(args):
     flops = causal_flops(B, H, S, D) if not doc_len else (S // doc_len) * causal_flops(B, H, doc_len, D)
     peaks = measured_peaks()
     checked = check_rows(api, torch, dist, w, rank, P, rows, dq, dk, dv, out, dev) if args.check_rows else None
+    schedule = None
+    launches_per_pass = P
+    if P > 1:
+        schedule = args.schedule if args.schedule != "auto" else (
+            "gather" if dk.numel() * dk.element_size() <= (32 << 20) else "ring")
+        if schedule == "gather":  # own shard, then the other P-1 shards 16 key segments per launch
+            per_launch = max(1, 16 // (w["n_splits"] if layout == 1 else 1))
+            launches_per_pass = 1 + -(-(P - 1) // per_launch)
     line = None
     if rank == 0:
         value = flops / (ms * 1e-3) / 1e12
@@ -337,18 +345,19 @@ def run_gpu_arm(args):
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "ra_prefill_host" if P == 1 else "pinned H2D + ra_ring_prefill + D2H per rank"},
-            "gpu_launches": K * P * P,  # one step kernel per ring step per pass on each of the P ranks
+            "gpu_launches": K * P * launches_per_pass,  # step kernels per pass on each of the P ranks
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                         "frac": per_gpu / peaks["tflops"], "traffic": None,
+                         "frac": per_gpu / peaks["tflops"],
+                         # ncu, one launch of this workload at N = 1 (profiles/step_tc_kernel_config2_prefill.md)
+                         "traffic": 215.0e6 if (P == 1 and args.workload == "config2") else None,
+                         "traffic_unit": "bytes per launch (dram read + write, ncu)",
                          "peak_source": f"{peaks['source']} bf16 GEMM burst",
-                         "kernel": f"step_tc_kernel<{D}> (one launch per ring step)"},
+                         "kernel": f"step_tc_kernel<{D}>"},
             "device_status": status,
             "ring": {"total_ms": ring_times[0], "comp_ms": ring_times[1], "comm_ms": ring_times[2],
                      "wait_ms": ring_times[3], "exposed_comm_frac": ring_times[3] / max(ring_times[0], 1e-9),
-                     "schedule": (args.schedule if args.schedule != "auto" else
-                                  ("gather" if dk.numel() * dk.element_size() <= (32 << 20) else "ring"))
-                     if P > 1 else None,
+                     "schedule": schedule, "step_launches_per_pass": launches_per_pass,
                      "note": "one pass, max over ranks; wait = pass time not covered by step kernels"},
         }
         if checked is not None:
@@ -444,7 +453,12 @@ def bench_decode(api, torch, dev, args, peaks):
     return {"workload": "decode B4 H32 kvH8 D128 fp16, 262144 cached tokens, cp_size 1 (config 4)",
             "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "hbm_gbs": gbs,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                         "frac": gbs / peaks["hbm_gbs"],
+                         # ncu on a quarter of this cache (1.0738 GB read + 5.1 MB written per launch),
+                         # scaled by 4: traffic is proportional to the cached length
+                         # (profiles/decode_mma_kernel_config4_decode.md)
+                         "traffic": 4 * (1.0738e9 + 5.1e6),
+                         "traffic_unit": "bytes per launch (dram read + write, ncu, scaled x4)",
                          "peak_source": f"{peaks['source']} copy bandwidth",
                          "algorithmic_bytes": kv_bytes},
             "gpu_launches_per_step": 4}
