@@ -125,5 +125,9 @@ int decode_step(int dtype, const void* q, const void* k, const void* v, float* o
 int launch_init(float* out, float* m, float* l, size_t out_count, size_t m_count,
                 cudaStream_t stream);
 int launch_finalize(float* out, const float* l, size_t rows, int D, cudaStream_t stream);
+// Merge up to 8 online-softmax states of the same rows ([O | m | l] blocks part_stride floats
+// apart, rows * D + rows even multiples of 4 floats so every O stays 16-byte aligned).
+int launch_state_merge(const float* parts, size_t part_stride, int n_parts, size_t rows, int D,
+                       float* out, float* m_out, float* l_out, int normalise, cudaStream_t stream);
 
 }  // namespace rab

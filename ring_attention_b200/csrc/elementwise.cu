@@ -196,6 +196,52 @@ __global__ void partial_merge_kernel(const float* __restrict__ gathered, float* 
   }
 }
 
+// Merge n_parts online-softmax states of the same rows, each laid out [O rows*D | m rows | l rows]
+// and part_stride floats apart, into out / m_out / l_out. One thread per float4 of a row.
+constexpr int kMaxStateParts = 8;
+__global__ void state_merge_kernel(const float* __restrict__ parts, size_t part_stride, int n_parts,
+                                   size_t rows, int D, float* __restrict__ out,
+                                   float* __restrict__ m_out, float* __restrict__ l_out,
+                                   int normalise) {
+  const int vec = D / 4;
+  const size_t total = rows * vec;
+  const size_t step = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += step) {
+    const size_t row = idx / vec;
+    const int c = static_cast<int>(idx - row * vec);
+    float sc[kMaxStateParts];
+    float m_max = -INFINITY;
+    for (int p = 0; p < n_parts; ++p) {
+      sc[p] = parts[p * part_stride + rows * D + row];
+      m_max = fmaxf(m_max, sc[p]);
+    }
+    float l_acc = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < n_parts; ++p) {
+      const float w = (sc[p] == -INFINITY) ? 0.f : expf(sc[p] - m_max);
+      l_acc += w * parts[p * part_stride + rows * D + rows + row];
+      const float4 o = *reinterpret_cast<const float4*>(parts + p * part_stride + row * D + 4 * c);
+      acc.x += w * o.x;
+      acc.y += w * o.y;
+      acc.z += w * o.z;
+      acc.w += w * o.w;
+    }
+    if (normalise) {
+      const float inv = l_acc > 0.f ? 1.f / l_acc : 0.f;
+      acc.x *= inv;
+      acc.y *= inv;
+      acc.z *= inv;
+      acc.w *= inv;
+    }
+    *reinterpret_cast<float4*>(out + row * D + 4 * c) = acc;
+    if (c == 0) {
+      if (m_out) m_out[row] = m_max;
+      if (l_out) l_out[row] = l_acc;
+    }
+  }
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -206,6 +252,18 @@ int launch_init(float* out, float* m, float* l, size_t out_count, size_t m_count
   const size_t o_work = vec_ok ? out_count / 4 : out_count;
   const size_t work = o_work > m_count ? o_work : m_count;
   init_kernel<<<grid_for(work, 256), 256, 0, stream>>>(out, m, l, out_count, m_count, vec_ok);
+  RAB_CUDA(cudaGetLastError());
+  return RA_OK;
+}
+
+int launch_state_merge(const float* parts, size_t part_stride, int n_parts, size_t rows, int D,
+                       float* out, float* m_out, float* l_out, int normalise, cudaStream_t stream) {
+  RAB_REQUIRE(parts && out && n_parts >= 1 && n_parts <= kMaxStateParts && D % 4 == 0 &&
+                  part_stride % 4 == 0 && aligned16(parts) && aligned16(out),
+              RA_ERR_INVALID, "state merge: bad arguments");
+  if (rows == 0) return RA_OK;
+  state_merge_kernel<<<grid_for(rows * (D / 4), 256), 256, 0, stream>>>(
+      parts, part_stride, n_parts, rows, D, out, m_out, l_out, normalise);
   RAB_CUDA(cudaGetLastError());
   return RA_OK;
 }

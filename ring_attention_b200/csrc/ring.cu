@@ -87,6 +87,8 @@ bool load_nccl() {
   } while (0)
 
 constexpr int kMaxRanks = 64;
+constexpr int kAuxStreams = 3;
+constexpr int kMaxKeyParts = 7;  // + the own-shard state = the 8 states one merge takes
 
 }  // namespace
 }  // namespace rab
@@ -98,6 +100,9 @@ struct ra_ring {
   ncclComm_t comm;
   bool own_comm;
   cudaStream_t comm_stream;
+  cudaStream_t aux_stream[kAuxStreams];  // key-split launches of the gather schedule
+  cudaEvent_t ev_aux[kAuxStreams];
+  int sm_count;
   cudaEvent_t ev_start, ev_end;
   cudaEvent_t ev_comm[kMaxRanks], ev_comm_begin[kMaxRanks];
   cudaEvent_t ev_comp[kMaxRanks], ev_comp_begin[kMaxRanks];
@@ -123,6 +128,13 @@ static int ring_finish_create(int rank, int cp, ncclComm_t comm, bool own, ra_ri
   int prio_lo = 0, prio_hi = 0;
   RAB_CUDA(cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi));
   RAB_CUDA(cudaStreamCreateWithPriority(&r->comm_stream, cudaStreamNonBlocking, prio_hi));
+  int dev = 0;
+  RAB_CUDA(cudaGetDevice(&dev));
+  RAB_CUDA(cudaDeviceGetAttribute(&r->sm_count, cudaDevAttrMultiProcessorCount, dev));
+  for (int i = 0; i < kAuxStreams; ++i) {
+    RAB_CUDA(cudaStreamCreateWithFlags(&r->aux_stream[i], cudaStreamNonBlocking));
+    RAB_CUDA(cudaEventCreateWithFlags(&r->ev_aux[i], cudaEventDisableTiming));
+  }
   RAB_CUDA(cudaEventCreate(&r->ev_start));
   RAB_CUDA(cudaEventCreate(&r->ev_end));
   for (int i = 0; i < kMaxRanks; ++i) {
@@ -177,6 +189,11 @@ void ra_ring_destroy(ra_ring* r) {
   cudaStreamSynchronize(r->comm_stream);
   if (r->comm && r->own_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(r->comm);
   cudaStreamDestroy(r->comm_stream);
+  for (int i = 0; i < kAuxStreams; ++i) {
+    cudaStreamSynchronize(r->aux_stream[i]);
+    cudaStreamDestroy(r->aux_stream[i]);
+    cudaEventDestroy(r->ev_aux[i]);
+  }
   cudaEventDestroy(r->ev_start);
   cudaEventDestroy(r->ev_end);
   for (int i = 0; i < kMaxRanks; ++i) {
@@ -225,6 +242,44 @@ static bool use_gather(const ra_ring* r, const ra_ring_config* c, size_t kv_raw)
   return kv_raw <= kGatherMaxBytes;
 }
 
+// How the gather schedule folds the other ranks' shards. Their key segments ("entries": shard
+// s hops away, sub-group i) are dealt round-robin to `parts` launches that run side by side on
+// their own streams, each into its own partial state, merged at the end. More than one part is
+// used when one launch cannot name all entries (RA_MAX_SEG) or when the query blocks alone do
+// not fill the GPU twice over: a block's loop over every gathered key is then the critical
+// path of the pass, and splitting the keys shortens it.
+struct GatherPlan {
+  bool stacked;        // false: one plain step per shard (fp32, head_dim 32 / 256)
+  int nsg;             // key segments per shard
+  int entries;         // (cp - 1) * nsg
+  int parts;           // launches over the entries
+  size_t part_floats;  // floats of one partial state [O | m | l]
+};
+
+static GatherPlan gather_plan(const ra_ring* r, const ra_ring_config* c) {
+  GatherPlan g;
+  g.nsg = c->layout == 1 ? c->n_splits : 1;
+  g.entries = (r->cp - 1) * g.nsg;
+  const int sloc = c->seq / r->cp;
+  const int seg_len = sloc / g.nsg;
+  const size_t rows = static_cast<size_t>(c->batch) * c->heads * sloc;
+  g.part_floats = (rows * c->head_dim + 2 * rows + 3) & ~static_cast<size_t>(3);
+  g.parts = 1;
+  g.stacked = step_stacked_supported(c->dtype, c->head_dim);
+  if (g.stacked) {
+    const int need = (g.entries + RA_MAX_SEG - 1) / RA_MAX_SEG;
+    const long long blocks =
+        static_cast<long long>(c->batch) * c->heads * g.nsg * ((seg_len + 255) / 256);
+    long long want = (2ll * r->sm_count + blocks - 1) / blocks;
+    if (want > 4) want = 4;
+    g.parts = need > want ? need : static_cast<int>(want);
+    if (g.parts > g.entries) g.parts = g.entries;
+    if (g.parts > kMaxKeyParts) g.stacked = false;
+  }
+  if (!g.stacked) g.parts = 1;
+  return g;
+}
+
 size_t ra_ring_prefill_workspace_bytes(const ra_ring* r, const ra_ring_config* c) {
   if (!r || !c || r->cp <= 0) return 0;
   const int kvH = c->kv_heads > 0 ? c->kv_heads : c->heads;
@@ -234,8 +289,13 @@ size_t ra_ring_prefill_workspace_bytes(const ra_ring* r, const ra_ring_config* c
   const size_t kv_bytes = align256(kv_raw);
   const size_t ml = align256(static_cast<size_t>(c->batch) * c->heads * sloc * sizeof(float));
   size_t kv = 0;
-  if (r->cp > 1)
-    kv = use_gather(r, c, kv_raw) ? 2 * align256(static_cast<size_t>(r->cp) * kv_raw) : 4 * kv_bytes;
+  if (r->cp > 1 && use_gather(r, c, kv_raw)) {
+    kv = 2 * align256(static_cast<size_t>(r->cp) * kv_raw);
+    const GatherPlan g = gather_plan(r, c);
+    if (g.parts >= 2) kv += align256((g.parts + 1) * g.part_floats * sizeof(float));
+  } else if (r->cp > 1) {
+    kv = 4 * kv_bytes;
+  }
   return kv + 2 * ml + 256;
 }
 
@@ -260,10 +320,17 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
   const bool gather = use_gather(r, c, kv_raw);
   unsigned char* buf_k[2] = {nullptr, nullptr};
   unsigned char* buf_v[2] = {nullptr, nullptr};
+  GatherPlan plan{};
+  float* part_base = nullptr;
   if (P > 1 && gather) {
     buf_k[0] = base;  // every rank's K shard, rank-major
     buf_v[0] = base + align256(static_cast<size_t>(P) * kv_raw);
     base += 2 * align256(static_cast<size_t>(P) * kv_raw);
+    plan = gather_plan(r, c);
+    if (plan.parts >= 2) {
+      part_base = reinterpret_cast<float*>(base);
+      base += align256((plan.parts + 1) * plan.part_floats * sizeof(float));
+    }
   } else if (P > 1) {
     buf_k[0] = base;
     buf_v[0] = base + kv_bytes;
@@ -287,65 +354,96 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
     RAB_NCCL(g_nccl.GroupEnd());
     RAB_CUDA(cudaEventRecord(r->ev_comm[0], r->comm_stream));
   }
-  int n_launch = 0;  // step kernels of this pass, for the event timings
+  int n_launch = 0;  // timed compute intervals of this pass
   if (gather) {
+    const bool split = plan.parts >= 2;
+    auto part_out = [&](int p) { return part_base + static_cast<size_t>(p) * plan.part_floats; };
+    auto part_m = [&](int p) { return part_out(p) + rows * c->head_dim; };
+    auto part_l = [&](int p) { return part_m(p) + rows; };
     // step 0 on the rank's own shard while the all-gather runs
     ra_segmap qmap, kmap;
     int stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, 0, &qmap, &kmap);
-    RAB_REQUIRE(stride >= 1, RA_ERR_INVALID, "ring prefill: bad partition");
+    RAB_REQUIRE(stride >= 1 && kmap.n_seg == plan.nsg, RA_ERR_INVALID,
+                "ring prefill: bad partition");
     const unsigned causal_flag = c->causal ? RA_STEP_CAUSAL : 0u;
     RAB_CUDA(cudaEventRecord(r->ev_comp_begin[0], stream));
-    rc = ra_attention_step_ex(c->dtype, q, k, v, out, m, l, &shape, &qmap, &kmap, stride,
+    rc = ra_attention_step_ex(c->dtype, q, k, v, split ? part_out(0) : out, split ? part_m(0) : m,
+                              split ? part_l(0) : l, &shape, &qmap, &kmap, stride,
                               causal_flag | RA_STEP_FRESH, c->doc_len, 0, stream);
     if (rc != RA_OK) return rc;
     RAB_CUDA(cudaEventRecord(r->ev_comp[0], stream));
-    n_launch = 1;
     RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[0], 0));
-    // The other P-1 shards, as many per launch as the segment table holds: one launch sees
-    // their key segments side by side, so a query block's loop runs over all of them and the
-    // launch has one tail instead of one per shard. Where the kernel that reads stacked
-    // shards does not apply (fp32, head_dim 32 / 256) every shard gets its own step.
-    const int nsg = kmap.n_seg;
-    const bool stacked = step_stacked_supported(c->dtype, c->head_dim);
-    const int per_launch = stacked ? (RA_MAX_SEG / nsg > 0 ? RA_MAX_SEG / nsg : 1) : 1;
-    for (int s0 = 1; s0 < P; s0 += per_launch) {
-      const int g = (P - s0 < per_launch) ? P - s0 : per_launch;
-      unsigned flags = causal_flag | (s0 + g == P ? RA_STEP_FINALIZE : 0u);
-      RAB_REQUIRE(n_launch < kMaxRanks, RA_ERR_INVALID, "ring prefill: too many launches");
-      RAB_CUDA(cudaEventRecord(r->ev_comp_begin[n_launch], stream));
-      if (stacked) {
+    RAB_CUDA(cudaEventRecord(r->ev_comp_begin[1], stream));
+    if (!plan.stacked) {
+      // one plain step per shard, in ring order
+      for (int s = 1; s < P; ++s) {
+        const size_t src = static_cast<size_t>((r->rank - s + P) % P);
+        ra_segmap kq, ks;
+        stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s, &kq, &ks);
+        RAB_REQUIRE(stride >= 1, RA_ERR_INVALID, "ring prefill: bad partition");
+        rc = ra_attention_step_ex(c->dtype, q, buf_k[0] + src * kv_raw, buf_v[0] + src * kv_raw, out,
+                                  m, l, &shape, &kq, &ks, stride,
+                                  causal_flag | (s == P - 1 ? RA_STEP_FINALIZE : 0u), c->doc_len, 0,
+                                  stream);
+        if (rc != RA_OK) return rc;
+      }
+    } else {
+      // entry e = (s - 1) * nsg + i: sub-group i of the shard s hops away; part z takes the
+      // entries e = z, z + parts, ... so every part sees keys from all over the sequence
+      bool aux_used[kAuxStreams] = {false, false, false};
+      for (int z = 0; z < plan.parts; ++z) {
         PosMap km;
         std::memset(&km, 0, sizeof(km));
-        km.n_seg = g * nsg;
         km.seg_len = kmap.seg_len;
         int seg_shard[RA_MAX_SEG], seg_row[RA_MAX_SEG];
-        for (int t = 0; t < g; ++t) {
-          ra_segmap kq, ks;
-          stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s0 + t, &kq, &ks);
-          RAB_REQUIRE(stride >= 1 && ks.n_seg == nsg && ks.seg_len == kmap.seg_len, RA_ERR_INVALID,
-                      "ring prefill: bad partition");
-          for (int i = 0; i < nsg; ++i) {
-            km.base[t * nsg + i] = ks.base[i];
-            seg_shard[t * nsg + i] = (r->rank - (s0 + t) + P) % P;  // the shard s hops away
-            seg_row[t * nsg + i] = i * kmap.seg_len;
+        int last_s = -1;
+        ra_segmap kq, ks;
+        for (int e = z; e < plan.entries; e += plan.parts) {
+          const int s = 1 + e / plan.nsg, i = e % plan.nsg;
+          if (s != last_s) {
+            stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s, &kq, &ks);
+            RAB_REQUIRE(stride >= 1 && ks.n_seg == plan.nsg && ks.seg_len == kmap.seg_len,
+                        RA_ERR_INVALID, "ring prefill: bad partition");
+            last_s = s;
           }
+          RAB_REQUIRE(km.n_seg < RA_MAX_SEG, RA_ERR_INVALID, "ring prefill: too many segments");
+          km.base[km.n_seg] = ks.base[i];
+          seg_shard[km.n_seg] = (r->rank - s + P) % P;
+          seg_row[km.n_seg] = i * kmap.seg_len;
+          ++km.n_seg;
         }
         ra_shape sh = shape;
         sh.seq_k = km.n_seg * km.seg_len;
-        rc = step_stacked(c->dtype, q, buf_k[0], buf_v[0], out, m, l, sh, make_posmap(qmap), km,
-                          seg_shard, seg_row, P, sloc, stride, flags, c->doc_len, stream);
-      } else {
-        const size_t src = static_cast<size_t>((r->rank - s0 + P) % P);
-        ra_segmap kq, ks;
-        stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s0, &kq, &ks);
-        RAB_REQUIRE(stride >= 1, RA_ERR_INVALID, "ring prefill: bad partition");
-        rc = ra_attention_step_ex(c->dtype, q, buf_k[0] + src * kv_raw, buf_v[0] + src * kv_raw, out,
-                                  m, l, &shape, &kq, &ks, stride, flags, c->doc_len, 0, stream);
+        cudaStream_t st = stream;
+        if (z > 0) {
+          const int a = (z - 1) % kAuxStreams;
+          st = r->aux_stream[a];
+          if (!aux_used[a]) {
+            RAB_CUDA(cudaStreamWaitEvent(st, r->ev_start, 0));
+            RAB_CUDA(cudaStreamWaitEvent(st, r->ev_comm[0], 0));
+            aux_used[a] = true;
+          }
+        }
+        const unsigned flags = split ? (causal_flag | RA_STEP_FRESH) : (causal_flag | RA_STEP_FINALIZE);
+        rc = step_stacked(c->dtype, q, buf_k[0], buf_v[0], split ? part_out(z + 1) : out,
+                          split ? part_m(z + 1) : m, split ? part_l(z + 1) : l, sh,
+                          make_posmap(qmap), km, seg_shard, seg_row, P, sloc, stride, flags,
+                          c->doc_len, st);
+        if (rc != RA_OK) return rc;
       }
-      if (rc != RA_OK) return rc;
-      RAB_CUDA(cudaEventRecord(r->ev_comp[n_launch], stream));
-      ++n_launch;
+      if (split) {
+        for (int a = 0; a < kAuxStreams; ++a) {
+          if (!aux_used[a]) continue;
+          RAB_CUDA(cudaEventRecord(r->ev_aux[a], r->aux_stream[a]));
+          RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_aux[a], 0));
+        }
+        rc = launch_state_merge(part_base, plan.part_floats, plan.parts + 1, rows, c->head_dim, out,
+                                m, l, 1, stream);
+        if (rc != RA_OK) return rc;
+      }
     }
+    RAB_CUDA(cudaEventRecord(r->ev_comp[1], stream));
+    n_launch = 2;
   }
   for (int s = 0; s < P && !gather; ++s) {
     const void* cur_k = s == 0 ? k : buf_k[(s - 1) & 1];

@@ -28,7 +28,7 @@ def _worker(rank, world, port, case, ret):
         rng = np.random.default_rng(77)
         if case["kind"] == "prefill":
             B, H, kvH, S, D = case["B"], case["H"], case["kvH"], case["S"], case["D"]
-            dt = torch.float16
+            dt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[case.get("dtype", "f16")]
             q = torch.from_numpy(rng.standard_normal((B, H, S, D)).astype(np.float32)).to(dt)
             k = torch.from_numpy(rng.standard_normal((B, kvH, S, D)).astype(np.float32)).to(dt)
             v = torch.from_numpy(rng.standard_normal((B, kvH, S, D)).astype(np.float32)).to(dt)
@@ -54,7 +54,8 @@ def _worker(rank, world, port, case, ret):
                 want = oracle.cpu_attention(qf, kf, vf, case["causal"], kv_heads=kvH)
             got = out.cpu().numpy()
             w = want[:, :, rows.numpy()]
-            bad = np.abs(got - w) > 1e-3 + 1e-3 * np.abs(w)
+            tol = {"f16": 1e-3, "bf16": 8e-3, "f32": 1e-5}[case.get("dtype", "f16")]
+            bad = np.abs(got - w) > tol + tol * np.abs(w)
             ret[rank] = (int(bad.sum()), float(np.abs(got - w).max()), res.total_ms, res.comp_ms, res.comm_ms)
         else:
             B, H, kvH, D, prompt, steps = 2, 8, 2, 128, 4 * world * 16, 5
@@ -128,6 +129,16 @@ def test_ring_prefill_d128_noncausal_and_documents():
     for schedule in ("ring", "gather"):
         _run(world, dict(kind="prefill", B=1, H=2, kvH=2, S=S, D=128, causal=True, layout=1, n_splits=4,
                          doc_len=S // 4, schedule=schedule))
+
+
+@pytest.mark.parametrize("schedule", ["ring", "gather"])
+def test_ring_prefill_fp32_and_bf16(schedule):
+    # fp32 takes the SIMT step (and, gathered, one plain step per shard); bf16 the tensor-core one
+    world = _world()
+    _run(world, dict(kind="prefill", B=1, H=2, kvH=1, S=world * 2 * 96, D=64, causal=True, layout=1, n_splits=2,
+                     schedule=schedule, dtype="f32"))
+    _run(world, dict(kind="prefill", B=1, H=2, kvH=2, S=world * 2 * 160, D=128, causal=True, layout=2, n_splits=2,
+                     schedule=schedule, dtype="bf16"))
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16"])
