@@ -159,13 +159,20 @@ RA_API int ra_float_to_int8(const float* src, signed char* dst, size_t n, ra_str
 RA_API int ra_int8_to_float(const signed char* src, float* dst, size_t n, ra_stream stream);
 
 /* Whole single-GPU attention, fp32 in and out, end-aligned causal mask
- * (j <= i + seq_k - seq_q). Replace launch_flash_attention, launch_flash_attention_fp16
- * and launch_naive_attention (src/attention.hpp:42-65). `workspace` must hold
+ * (j <= i + seq_k - seq_q). Replaces launch_flash_attention and launch_flash_attention_fp16
+ * (src/attention.hpp:48-65). `workspace` must hold
  * ra_flash_workspace_bytes(shape, half_precision) bytes of device memory. */
 RA_API size_t ra_flash_workspace_bytes(const ra_shape* shape, int half_precision);
 RA_API int ra_flash_attention(const float* q, const float* k, const float* v, float* out,
                               const ra_shape* shape, int causal, int half_precision,
                               void* workspace, size_t workspace_bytes, ra_stream stream);
+
+/* Whole single-GPU attention for ANY head_dim (1..1024), fp32 end to end, same mask as
+ * ra_flash_attention. Replaces launch_naive_attention (src/attention.hpp:42-46,
+ * src/naive_attention.cu), the reference's correctness baseline, which its tests call with
+ * head sizes the tiled kernels do not take (16, 24). Not a fast path. */
+RA_API int ra_naive_attention(const float* q, const float* k, const float* v, float* out,
+                              const ra_shape* shape, int causal, ra_stream stream);
 
 /* Whole attention on HOST buffers (pinned or pageable), fp16/bf16/fp32 Q/K/V in, fp32 out:
  * uploads, runs init + step + finalize on the current device, downloads and

@@ -80,6 +80,7 @@ _SIG = {
                                             C.POINTER(SegMap), C.POINTER(SegMap),
                                             C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int,
                                             C.c_int, C.c_int, C.c_uint, C.c_longlong, _P]),
+    "ra_naive_attention": (C.c_int, [_P, _P, _P, _P, C.POINTER(Shape), C.c_int, _P]),
     "ra_attention_finalize": (C.c_int, [_P, _P, C.POINTER(Shape), _P]),
     "ra_attention_lse": (C.c_int, [_P, _P, _P, C.c_size_t, _P]),
     "ra_float_to_half": (C.c_int, [_P, _P, C.c_size_t, _P]),

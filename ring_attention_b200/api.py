@@ -172,8 +172,9 @@ def launch_flash_attention_fp16(q, k, v, out, shape, causal):
 
 
 def launch_naive_attention(q, k, v, out, shape, causal):
-    """``launch_naive_attention`` (reference src/attention.hpp:42-43): same result, fp32 path."""
-    _flash(q, k, v, out, shape, causal, False)
+    """``launch_naive_attention`` (reference src/attention.hpp:42-46): any head_dim, fp32."""
+    check(lib().ra_naive_attention(_ptr(q), _ptr(k), _ptr(v), _ptr(out), C.byref(shape.c()), int(causal),
+                                   _stream()))
 
 
 def prefill_host(q, k, v, shape, qmap, kmap, pos_stride=1, causal=False, doc_len=0,

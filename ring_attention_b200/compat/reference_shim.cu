@@ -83,7 +83,8 @@ void flash(const float* q, const float* k, const float* v, float* out, const Att
 
 void launch_naive_attention(const float* q, const float* k, const float* v, float* out,
                             const AttentionShape& s, bool causal, cudaStream_t stream) {
-  flash(q, k, v, out, s, causal, false, stream, "launch_naive_attention");
+  const ra_shape c = to_c(s);
+  must(ra_naive_attention(q, k, v, out, &c, causal ? 1 : 0, stream), "launch_naive_attention");
 }
 void launch_flash_attention(const float* q, const float* k, const float* v, float* out,
                             const AttentionShape& s, bool causal, cudaStream_t stream) {

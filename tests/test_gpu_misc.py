@@ -75,6 +75,23 @@ def test_flash_attention_entry_points(cfg, causal):
     assert_close(out.cpu().numpy(), oracle.cpu_attention(qh, kh, vh, causal, kv_heads=kvH), 1e-3, 1e-3, "fp16")
 
 
+# reference tests/test_naive_attention.cu:78-101: head sizes 16 and 24, Sq < Sk, GQA / MQA
+@pytest.mark.parametrize("cfg", [(1, 1, 1, 8, 8, 16), (2, 4, 4, 32, 32, 32), (1, 2, 2, 16, 48, 24),
+                                 (1, 1, 1, 64, 64, 64), (1, 8, 2, 32, 32, 32), (1, 4, 1, 32, 32, 32),
+                                 (1, 2, 1, 130, 300, 200), (1, 1, 1, 5, 3, 7)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_naive_attention_takes_any_head_dim(cfg, causal):
+    B, H, kvH, Sq, Sk, D = cfg
+    q, k, v = normal_inputs(78, B, H, kvH, Sq, Sk, D)
+    out = torch.full((B, H, Sq, D), float("nan"), device="cuda")
+    api.launch_naive_attention(dev(q), dev(k), dev(v), out, api.AttentionShape(B, H, Sq, Sk, D, kvH), causal)
+    want = oracle.cpu_attention(q, k, v, causal, kv_heads=kvH)
+    if causal and Sq > Sk:  # rows that see no key: zeros here, whatever the oracle's 0/0 gives
+        hidden = np.arange(Sq) + (Sk - Sq) < 0
+        want[:, :, hidden] = 0.0
+    assert_close(out.cpu().numpy(), want, 1e-5, 1e-5)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 def test_prefill_on_host_buffers(dtype):
     B, H, S, D = 1, 4, 512, 64

@@ -30,7 +30,7 @@ def test_reference_host_programs(name, expect):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("name,expect", [
-    ("test_smoke", None), ("test_device_tensor", None),
+    ("test_smoke", None), ("test_device_tensor", None), ("test_naive_attention", None),
     ("test_attention_step", "attention_step OK"), ("test_attention_step_fp16", "attention_step_fp16 OK"),
     ("test_attention_step_segmented", None), ("test_flash_attention", None),
     ("test_flash_attention_fp16", None), ("test_kv_cache", None), ("test_decode_op", None)])
