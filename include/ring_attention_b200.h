@@ -263,6 +263,13 @@ RA_API int ra_partition_position_stride(int cp_size, int mode);
 RA_API int ra_partition_next_rank(int cp_size, int rank);
 RA_API int ra_partition_prev_rank(int cp_size, int rank);
 
+/* Hierarchical (2-D) ring visitation order: the global rank whose shard GPU (node, local) of a
+ * num_nodes x gpus_per_node cluster holds at macro-step m (0..num_nodes-1), inner round i
+ * (0..gpus_per_node-1); global rank = node * gpus_per_node + local. Replaces
+ * Ring2DSchedule::source (src/ring2d_schedule.hpp:42-44, src/ring2d_schedule.cpp:30-42).
+ * Pure integer arithmetic, host only; -1 on arguments out of range. */
+RA_API int ra_ring2d_source(int num_nodes, int gpus_per_node, int node, int local, int m, int i);
+
 /* Fills the segment maps a rank uses at one ring step: qmap = its own sub-groups, kmap =
  * the sub-groups of the shard it holds at `step` (source (rank - step) mod cp_size,
  * src/ring_partition.cpp:64-68). Returns the position stride. Host only. */

@@ -224,3 +224,10 @@ class Partition:
         if self.impl == "port":
             return self.lib.orc_part_prev_rank(self.cp, self.rank)
         return self.lib.ref_part_prev_rank(self.cp, self.rank, self.seq)
+
+
+def ring2d_source(num_nodes, gpus_per_node, node, local, m, i, impl="port"):
+    """Shard (global rank) that GPU (node, local) holds at macro-step m, inner round i of the
+    hierarchical ring (reference src/ring2d_schedule.cpp:30-42); port or compiled reference."""
+    fn = port().orc_ring2d_source if impl == "port" else ref().ref_ring2d_source
+    return int(fn(num_nodes, gpus_per_node, node, local, m, i))

@@ -299,3 +299,13 @@ ORC_API int orc_part_num_sub_groups(int mode, int n_splits) { return mode == 1 ?
 ORC_API int orc_part_position_stride(int cp, int mode) { return mode == 2 ? cp : 1; }
 ORC_API int orc_part_next_rank(int cp, int rank) { return (rank + 1) % cp; }
 ORC_API int orc_part_prev_rank(int cp, int rank) { return (rank - 1 + cp) % cp; }
+
+/* Hierarchical (2-D) ring visitation order (src/ring2d_schedule.cpp:30-42): the shard that
+ * GPU (node, local) of a num_nodes x gpus_per_node cluster holds at macro-step m, inner round
+ * i. The band of a node moves one node on per macro-step, and inside a macro-step shards move
+ * one local index on per inner round. Global rank = node * gpus_per_node + local. */
+ORC_API int orc_ring2d_source(int num_nodes, int gpus_per_node, int node, int local, int m, int i) {
+  const int from_node = ((node - m) % num_nodes + num_nodes) % num_nodes;
+  const int from_local = ((local - i) % gpus_per_node + gpus_per_node) % gpus_per_node;
+  return from_node * gpus_per_node + from_local;
+}

@@ -1,7 +1,7 @@
 // extern "C" doorway onto the reference's OWN host code, compiled from the
 // reference source tree where it lies (never copied here): cpu_attention /
 // XorShift32 (src/cpu_attention.cpp), RingPartition (src/ring_partition.cpp),
-// gen_elem (src/ring_gen.hpp). Built into oracle/_ref/libref_oracle.so by
+// gen_elem (src/ring_gen.hpp), Ring2DSchedule (src/ring2d_schedule.cpp). Built into oracle/_ref/libref_oracle.so by
 // oracle/Makefile. TEST INFRASTRUCTURE ONLY: used to validate the C restatement
 // in oracle.c and as the timed CPU baseline; the shipped library never loads it.
 #include <cstddef>
@@ -11,6 +11,7 @@
 
 #include "cpu_attention.hpp"
 #include "ring_gen.hpp"
+#include "ring2d_schedule.hpp"
 #include "ring_partition.hpp"
 
 using ring_attention::AttentionShape;
@@ -82,4 +83,8 @@ int ref_part_position_stride(int cp, int rank, int seq, int mode, int n_splits) 
 }
 int ref_part_next_rank(int cp, int rank, int seq) { return make(cp, rank, seq, 0, 2).next_rank(); }
 int ref_part_prev_rank(int cp, int rank, int seq) { return make(cp, rank, seq, 0, 2).prev_rank(); }
+
+int ref_ring2d_source(int num_nodes, int gpus_per_node, int node, int local, int m, int i) {
+  return ring_attention::Ring2DSchedule(num_nodes, gpus_per_node, node, local).source(m, i);
+}
 }

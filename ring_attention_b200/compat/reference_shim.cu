@@ -18,6 +18,7 @@
 #include "decode_op.hpp"
 #include "device_tensor.hpp"
 #include "kv_cache.hpp"
+#include "ring2d_schedule.hpp"
 #include "ring_partition.hpp"
 
 #include "../../include/ring_attention_b200.h"
@@ -287,6 +288,21 @@ void run_local_decode_step_fp16(const __half* q, const DeviceKVCache<__half>& ca
                                 int q_pos_global, int cache_k_offset, bool causal, float* out,
                                 cudaStream_t stream) {
   local_decode<__half>(RA_F16, q, cache, heads, q_pos_global, cache_k_offset, causal, out, stream);
+}
+
+// ---- src/ring2d_schedule.hpp -------------------------------------------------------------
+
+Ring2DSchedule::Ring2DSchedule(int num_nodes, int gpus_per_node, int node, int local)
+    : num_nodes_(num_nodes), gpus_per_node_(gpus_per_node), node_(node), local_(local) {
+  if (num_nodes <= 0 || gpus_per_node <= 0 || node < 0 || node >= num_nodes || local < 0 ||
+      local >= gpus_per_node) {
+    std::fprintf(stderr, "Ring2DSchedule: invalid arguments\n");
+    std::abort();
+  }
+  trace_.reserve(static_cast<std::size_t>(num_nodes) * gpus_per_node);
+  for (int m = 0; m < num_nodes; ++m)
+    for (int i = 0; i < gpus_per_node; ++i)
+      trace_.push_back(ra_ring2d_source(num_nodes, gpus_per_node, node, local, m, i));
 }
 
 // ---- src/ring_partition.hpp --------------------------------------------------------------

@@ -526,6 +526,17 @@ int ra_partition_position_stride(int cp, int mode) { return mode == 2 ? cp : 1; 
 int ra_partition_next_rank(int cp, int rank) { return (rank + 1) % cp; }
 int ra_partition_prev_rank(int cp, int rank) { return (rank - 1 + cp) % cp; }
 
+int ra_ring2d_source(int num_nodes, int gpus_per_node, int node, int local, int m, int i) {
+  if (num_nodes <= 0 || gpus_per_node <= 0 || node < 0 || node >= num_nodes || local < 0 ||
+      local >= gpus_per_node || m < 0 || m >= num_nodes || i < 0 || i >= gpus_per_node)
+    return -1;
+  // a node's band of shards moves on one node per macro-step; inside a macro-step the shards
+  // of the band move on one local index per inner round
+  const int band = (node + num_nodes - m) % num_nodes;
+  const int slot = (local + gpus_per_node - i) % gpus_per_node;
+  return band * gpus_per_node + slot;
+}
+
 int ra_ring_step_maps(int cp, int rank, int seq, int mode, int n_splits, int step,
                       ra_segmap* qmap, ra_segmap* kmap) {
   if (!qmap || !kmap || cp <= 0 || rank < 0 || rank >= cp) return -1;

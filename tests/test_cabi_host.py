@@ -129,3 +129,26 @@ def test_workspace_size_queries():
     assert lib().ra_decode_workspace_bytes(C.byref(s)) >= 4 * 32 * 130 * 4
     s2 = Shape(1, 8, 64, 64, 64, 0)
     assert lib().ra_flash_workspace_bytes(C.byref(s2), 1) > lib().ra_flash_workspace_bytes(C.byref(s2), 0)
+
+
+@pytest.mark.parametrize("N,G", [(1, 1), (1, 8), (8, 1), (2, 2), (2, 4), (3, 5), (4, 8)])
+def test_ring2d_schedule_bit_exact_and_covering(N, G):
+    """ra_ring2d_source against the oracle, plus the properties the reference's own test checks
+    (tests/test_ring2d_schedule.cpp:40-128): every shard exactly once, own shard first, one node's
+    band per macro-step."""
+    L = lib()
+    for n in range(N):
+        for g in range(G):
+            seen = []
+            for m in range(N):
+                nodes = set()
+                for i in range(G):
+                    src = L.ra_ring2d_source(N, G, n, g, m, i)
+                    assert src == oracle.ring2d_source(N, G, n, g, m, i)
+                    seen.append(src)
+                    nodes.add(src // G)
+                assert len(nodes) == 1
+            assert sorted(seen) == list(range(N * G))
+            assert seen[0] == n * G + g
+    for bad in [(0, 2, 0, 0, 0, 0), (2, 2, 2, 0, 0, 0), (2, 2, 0, 2, 0, 0), (2, 2, 0, 0, 2, 0), (2, 2, 0, 0, 0, -1)]:
+        assert L.ra_ring2d_source(*bad) == -1

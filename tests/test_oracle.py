@@ -244,3 +244,23 @@ def test_partial_merge_equals_joint_softmax():
     w = np.where(np.isinf(m_all), 0, np.exp(m_all - mm))
     want_l = sum(w[r] * blocks[r][BH * D + BH:] for r in range(cp))
     assert_close(l, want_l, 1e-6, 1e-6)
+
+
+def test_ring2d_known_trace_n2_g2():
+    # the exact visitation order the reference pins (tests/test_ring2d_schedule.cpp:150-158):
+    # sources[rank][m * G + i] on 2 nodes x 2 GPUs
+    expected = [[0, 1, 2, 3], [1, 0, 3, 2], [2, 3, 0, 1], [3, 2, 1, 0]]
+    for r in range(4):
+        got = [oracle.ring2d_source(2, 2, r // 2, r % 2, m, i) for m in range(2) for i in range(2)]
+        assert got == expected[r]
+
+
+@needs_ref
+@pytest.mark.parametrize("N,G", [(1, 1), (1, 8), (8, 1), (2, 2), (2, 4), (3, 5), (4, 8)])
+def test_port_ring2d_equals_reference(N, G):
+    for n in range(N):
+        for g in range(G):
+            for m in range(N):
+                for i in range(G):
+                    assert (oracle.ring2d_source(N, G, n, g, m, i) ==
+                            oracle.ring2d_source(N, G, n, g, m, i, impl="ref"))

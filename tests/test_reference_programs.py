@@ -22,6 +22,7 @@ def run(name, timeout=600):
 
 
 @pytest.mark.parametrize("name,expect", [("test_ring_partition", "All ring_partition tests passed"),
+                                         ("test_ring2d_schedule", "All ring2d_schedule tests passed"),
                                          ("test_cpu_attention", "cpu_attention OK"),
                                          ("test_gen_elem", "All gen_elem tests passed")])
 def test_reference_host_programs(name, expect):
