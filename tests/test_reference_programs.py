@@ -102,3 +102,12 @@ def test_reference_cli_decode_benchmark_csv():
     out = mpirun(2, "ring_attention_cli", "--run", "decode", "--prompt-len", "64", "--decode-tokens", "3",
                  "--batch", "1", "--heads", "2", "--head_dim", "32", "--csv-header", "--csv")
     assert re.search(r"decode summary[^\n]*cp_size=2", out), out[-1500:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1, 2])
+def test_reference_hello_mpi_cuda(n):
+    # apps/hello_mpi_cuda: every rank reports itself (the reference's launcher sanity check)
+    out = mpirun(n, "hello_mpi_cuda")
+    for r in range(n):
+        assert f"rank {r}/{n}" in out and "OK" in out, out[-800:]
