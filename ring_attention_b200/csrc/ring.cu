@@ -258,7 +258,7 @@ struct GatherPlan {
 
 static GatherPlan gather_plan(const ra_ring* r, const ra_ring_config* c) {
   GatherPlan g;
-  g.nsg = c->layout == 1 ? c->n_splits : 1;
+  g.nsg = (c->layout == 1 && c->n_splits >= 1) ? c->n_splits : 1;  // bad configs are rejected later
   g.entries = (r->cp - 1) * g.nsg;
   const int sloc = c->seq / r->cp;
   const int seg_len = sloc / g.nsg;
@@ -270,10 +270,10 @@ static GatherPlan gather_plan(const ra_ring* r, const ra_ring_config* c) {
     const int need = (g.entries + RA_MAX_SEG - 1) / RA_MAX_SEG;
     const long long blocks =
         static_cast<long long>(c->batch) * c->heads * g.nsg * ((seg_len + 255) / 256);
-    long long want = (2ll * r->sm_count + blocks - 1) / blocks;
+    long long want = blocks > 0 ? (2ll * r->sm_count + blocks - 1) / blocks : 1;
     if (want > 4) want = 4;
     g.parts = need > want ? need : static_cast<int>(want);
-    if (g.parts > g.entries) g.parts = g.entries;
+    if (g.parts > g.entries) g.parts = g.entries > 0 ? g.entries : 1;
     if (g.parts > kMaxKeyParts) g.stacked = false;
   }
   if (!g.stacked) g.parts = 1;
