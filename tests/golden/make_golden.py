@@ -26,7 +26,8 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+_BESIDE_REPO = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference"))
+REF = sys.argv[1] if len(sys.argv) > 1 else _BESIDE_REPO
 sys.path.insert(0, os.path.join(REF, "reference"))
 HERE = os.path.dirname(os.path.abspath(__file__))
 
