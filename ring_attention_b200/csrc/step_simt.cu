@@ -9,10 +9,12 @@
 // piecewise-affine maps, which covers the affine call (one segment), the segmented call
 // (src/attention_step.cu:305-460) and striped layouts (stride > 1).
 //
-// Layout of the work: a block owns 64 query rows; 4 threads share a row, each holding a
-// quarter of the head dimension of Q and of the output accumulator in registers. K/V tiles
-// of 4096/D keys are staged in shared memory as fp32; a score is a quarter dot product per
-// thread plus two shuffles.
+// Layout of the work: 256 threads per block, 4 to 16 threads share a query row (16 elements of
+// the head dimension each, 8 at head_dim 32) and every thread carries TWO rows, so a K or V
+// value read from shared memory feeds two multiply-adds and the inner loops are bound by the
+// FMA pipe (packed fp32x2 multiply-adds) instead of by shared-memory reads. K/V tiles of
+// 4096/D keys are staged in shared memory as fp32; a score is a partial dot product per thread
+// plus a shuffle reduction over the row's threads.
 #include <cfloat>
 
 #include "common.cuh"
@@ -21,10 +23,29 @@ namespace rab {
 
 namespace {
 
-constexpr int kRows = 64;
-constexpr int kThreadsPerRow = 4;
-constexpr int kThreads = kRows * kThreadsPerRow;
-constexpr int kChunk = 16;  // keys folded per online-softmax update
+constexpr int kThreads = 256;
+constexpr int kChunk = 8;   // keys folded per online-softmax update
+constexpr int kR = 2;       // query rows per thread
+
+template <int D>
+struct SimtCfg {
+  static constexpr int kTPR = D <= 64 ? 4 : D / 16;  // threads per row
+  static constexpr int kDQ = D / kTPR;               // head-dimension elements per thread
+  static constexpr int kGroups = kThreads / kTPR;    // row groups per block
+  static constexpr int kRows = kGroups * kR;         // query rows per block
+  static constexpr int kBC = 4096 / D;               // keys per shared-memory tile
+};
+
+// packed fp32x2 multiply-add: one instruction for two lanes
+__device__ inline float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)),
+        "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return d;
+}
 
 template <typename T>
 __device__ inline float load_as_float(const T* p);
@@ -67,14 +88,15 @@ __device__ inline int pos_of(const PosMap& pm, int i, int stride) {
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
     step_simt_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                      float* __restrict__ O, float* __restrict__ M, float* __restrict__ L, int H,
                      int kvH, int Sq, int Sk, long long kv_head_stride, PosMap qmap, PosMap kmap,
                      int stride, unsigned flags, long long doc_len) {
-  constexpr int DQ = D / kThreadsPerRow;  // elements of the head dimension per thread
-  constexpr int BC = 4096 / D;            // keys per shared-memory tile
+  using C = SimtCfg<D>;
+  constexpr int DQ = C::kDQ, BC = C::kBC, TPR = C::kTPR;
   static_assert(BC % kChunk == 0, "tile must be a whole number of chunks");
+  static_assert(DQ % 4 == 0, "float4 loads");
   __shared__ __align__(16) float Ks[BC * D];
   __shared__ __align__(16) float Vs[BC * D];
   __shared__ int kpos_s[BC];
@@ -83,54 +105,58 @@ __global__ void __launch_bounds__(kThreads)
   const bool causal = (flags & RA_STEP_CAUSAL) != 0;
   const bool fresh = (flags & RA_STEP_FRESH) != 0;
   const int tid = threadIdx.x;
-  const int r = tid / kThreadsPerRow;
-  const int c = tid % kThreadsPerRow;
+  const int g = tid / TPR;  // row group; its rows are g and g + kGroups of the block
+  const int c = tid % TPR;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
-  const int i = blockIdx.x * kRows + r;
-  const bool active = i < Sq;
   const float scale = rsqrtf(static_cast<float>(D));
 
   const size_t q_head = (static_cast<size_t>(b) * H + h) * static_cast<size_t>(Sq) * D;
   const size_t kv_head = (static_cast<size_t>(b) * kvH + (h % kvH)) * kv_head_stride;
-  const size_t row_idx = (static_cast<size_t>(b) * H + h) * Sq + (active ? i : 0);
 
-  const int qpos = active ? pos_of(qmap, i, stride) : INT_MIN;
-  const long long qdoc = (doc_len > 0 && active) ? qpos / doc_len : 0;
+  int row[kR], qpos[kR];
+  long long qdoc[kR];
+  bool active[kR];
+  size_t row_idx[kR];
+  float2 q2[kR][DQ / 2], o2[kR][DQ / 2];
+  float m_i[kR], l_i[kR];
 
   if (tid == 0) qmax_s = INT_MIN;
   __syncthreads();
-  if (active && c == 0) atomicMax(&qmax_s, qpos);
-
-  float q_reg[DQ], o_reg[DQ];
-  float m_i = -INFINITY, l_i = 0.f;
 #pragma unroll
-  for (int d = 0; d < DQ; ++d) {
-    q_reg[d] = 0.f;
-    o_reg[d] = 0.f;
-  }
-  if (active) {
-    const T* qp = Q + q_head + static_cast<size_t>(i) * D + c * DQ;
+  for (int rr = 0; rr < kR; ++rr) {
+    row[rr] = blockIdx.x * C::kRows + rr * C::kGroups + g;
+    active[rr] = row[rr] < Sq;
+    row_idx[rr] = (static_cast<size_t>(b) * H + h) * Sq + (active[rr] ? row[rr] : 0);
+    qpos[rr] = active[rr] ? pos_of(qmap, row[rr], stride) : INT_MIN;
+    qdoc[rr] = (doc_len > 0 && active[rr]) ? qpos[rr] / doc_len : 0;
+    m_i[rr] = -INFINITY;
+    l_i[rr] = 0.f;
 #pragma unroll
-    for (int d = 0; d < DQ; d += 4) {
-      const float4 x = load4<T>(qp + d);
-      q_reg[d] = x.x;
-      q_reg[d + 1] = x.y;
-      q_reg[d + 2] = x.z;
-      q_reg[d + 3] = x.w;
+    for (int d = 0; d < DQ / 2; ++d) {
+      q2[rr][d] = make_float2(0.f, 0.f);
+      o2[rr][d] = make_float2(0.f, 0.f);
     }
-    if (!fresh) {
-      const float* op = O + q_head + static_cast<size_t>(i) * D + c * DQ;
+    if (active[rr]) {
+      if (c == 0) atomicMax(&qmax_s, qpos[rr]);
+      const T* qp = Q + q_head + static_cast<size_t>(row[rr]) * D + c * DQ;
 #pragma unroll
       for (int d = 0; d < DQ; d += 4) {
-        const float4 x = *reinterpret_cast<const float4*>(op + d);
-        o_reg[d] = x.x;
-        o_reg[d + 1] = x.y;
-        o_reg[d + 2] = x.z;
-        o_reg[d + 3] = x.w;
+        const float4 x = load4<T>(qp + d);
+        q2[rr][d / 2] = make_float2(x.x, x.y);
+        q2[rr][d / 2 + 1] = make_float2(x.z, x.w);
       }
-      m_i = M[row_idx];
-      l_i = L[row_idx];
+      if (!fresh) {
+        const float* op = O + q_head + static_cast<size_t>(row[rr]) * D + c * DQ;
+#pragma unroll
+        for (int d = 0; d < DQ; d += 4) {
+          const float4 x = *reinterpret_cast<const float4*>(op + d);
+          o2[rr][d / 2] = make_float2(x.x, x.y);
+          o2[rr][d / 2 + 1] = make_float2(x.z, x.w);
+        }
+        m_i[rr] = M[row_idx[rr]];
+        l_i[rr] = L[row_idx[rr]];
+      }
     }
   }
   __syncthreads();
@@ -167,92 +193,122 @@ __global__ void __launch_bounds__(kThreads)
 
 #pragma unroll 1
     for (int jc = 0; jc < BC; jc += kChunk) {
-      float s[kChunk];
+      float s[kR][kChunk];
 #pragma unroll
       for (int jj = 0; jj < kChunk; ++jj) {
         const float* kr = &Ks[(jc + jj) * D + c * DQ];
-        float acc = 0.f;
+        float2 acc[kR];
+#pragma unroll
+        for (int rr = 0; rr < kR; ++rr) acc[rr] = make_float2(0.f, 0.f);
 #pragma unroll
         for (int d = 0; d < DQ; d += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
-          acc += q_reg[d] * k4.x + q_reg[d + 1] * k4.y + q_reg[d + 2] * k4.z +
-                 q_reg[d + 3] * k4.w;
-        }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        s[jj] = acc;
-      }
-      float m_new = m_i;
+          const float2 ka = make_float2(k4.x, k4.y), kb = make_float2(k4.z, k4.w);
 #pragma unroll
-      for (int jj = 0; jj < kChunk; ++jj) {
-        const int kp = kpos_s[jc + jj];
-        bool vis = (kp != INT_MAX) && (!causal || kp <= qpos);
-        if (doc_len > 0 && vis) vis = (kp / doc_len) == qdoc;
-        if (vis) {
-          s[jj] *= scale;
-          m_new = fmaxf(m_new, s[jj]);
-        } else {
-          s[jj] = -INFINITY;
+          for (int rr = 0; rr < kR; ++rr) {
+            acc[rr] = ffma2(q2[rr][d / 2], ka, acc[rr]);
+            acc[rr] = ffma2(q2[rr][d / 2 + 1], kb, acc[rr]);
+          }
+        }
+#pragma unroll
+        for (int rr = 0; rr < kR; ++rr) {
+          float a = acc[rr].x + acc[rr].y;
+#pragma unroll
+          for (int o = 1; o < TPR; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+          s[rr][jj] = a;
         }
       }
-      if (m_new == -INFINITY) continue;  // nothing visible so far: state unchanged
-      const float alpha = expf(m_i - m_new);
-      float row_sum = 0.f;
+      float alpha[kR];
+      bool live[kR];
 #pragma unroll
-      for (int jj = 0; jj < kChunk; ++jj) {
-        s[jj] = (s[jj] == -INFINITY) ? 0.f : expf(s[jj] - m_new);
-        row_sum += s[jj];
+      for (int rr = 0; rr < kR; ++rr) {
+        float m_new = m_i[rr];
+#pragma unroll
+        for (int jj = 0; jj < kChunk; ++jj) {
+          const int kp = kpos_s[jc + jj];
+          bool vis = (kp != INT_MAX) && (!causal || kp <= qpos[rr]);
+          if (doc_len > 0 && vis) vis = (kp / doc_len) == qdoc[rr];
+          if (vis) {
+            s[rr][jj] *= scale;
+            m_new = fmaxf(m_new, s[rr][jj]);
+          } else {
+            s[rr][jj] = -INFINITY;
+          }
+        }
+        live[rr] = m_new != -INFINITY;  // false: nothing visible so far, state unchanged
+        alpha[rr] = live[rr] ? expf(m_i[rr] - m_new) : 1.f;
+        float row_sum = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < kChunk; ++jj) {
+          s[rr][jj] = (s[rr][jj] == -INFINITY) ? 0.f : expf(s[rr][jj] - m_new);
+          row_sum += s[rr][jj];
+        }
+        if (live[rr]) {
+          l_i[rr] = alpha[rr] * l_i[rr] + row_sum;
+          m_i[rr] = m_new;
+          const float2 a2 = make_float2(alpha[rr], alpha[rr]);
+#pragma unroll
+          for (int d = 0; d < DQ / 2; ++d) o2[rr][d] = make_float2(o2[rr][d].x * a2.x, o2[rr][d].y * a2.y);
+        }
       }
+      bool any_live = false;
 #pragma unroll
-      for (int d = 0; d < DQ; ++d) o_reg[d] *= alpha;
+      for (int rr = 0; rr < kR; ++rr) any_live |= live[rr];
+      if (!any_live) continue;
 #pragma unroll
       for (int jj = 0; jj < kChunk; ++jj) {
-        const float p = s[jj];
         const float* vr = &Vs[(jc + jj) * D + c * DQ];
+        float2 p2[kR];
+#pragma unroll
+        for (int rr = 0; rr < kR; ++rr) p2[rr] = make_float2(s[rr][jj], s[rr][jj]);
 #pragma unroll
         for (int d = 0; d < DQ; d += 4) {
           const float4 v4 = *reinterpret_cast<const float4*>(vr + d);
-          o_reg[d] += p * v4.x;
-          o_reg[d + 1] += p * v4.y;
-          o_reg[d + 2] += p * v4.z;
-          o_reg[d + 3] += p * v4.w;
+          const float2 va = make_float2(v4.x, v4.y), vb = make_float2(v4.z, v4.w);
+#pragma unroll
+          for (int rr = 0; rr < kR; ++rr) {
+            o2[rr][d / 2] = ffma2(p2[rr], va, o2[rr][d / 2]);
+            o2[rr][d / 2 + 1] = ffma2(p2[rr], vb, o2[rr][d / 2 + 1]);
+          }
         }
       }
-      l_i = alpha * l_i + row_sum;
-      m_i = m_new;
     }
     __syncthreads();  // everyone is done with Ks/Vs/kpos_s before the next tile overwrites them
   }
 
-  if (active) {
+#pragma unroll
+  for (int rr = 0; rr < kR; ++rr) {
+    if (!active[rr]) continue;
     float inv = 1.f;
-    if (flags & RA_STEP_FINALIZE) inv = l_i > 0.f ? 1.f / l_i : 0.f;
-    float* op = O + q_head + static_cast<size_t>(i) * D + c * DQ;
+    if (flags & RA_STEP_FINALIZE) inv = l_i[rr] > 0.f ? 1.f / l_i[rr] : 0.f;
+    float* op = O + q_head + static_cast<size_t>(row[rr]) * D + c * DQ;
 #pragma unroll
     for (int d = 0; d < DQ; d += 4) {
-      *reinterpret_cast<float4*>(op + d) = make_float4(o_reg[d] * inv, o_reg[d + 1] * inv,
-                                                       o_reg[d + 2] * inv, o_reg[d + 3] * inv);
+      *reinterpret_cast<float4*>(op + d) =
+          make_float4(o2[rr][d / 2].x * inv, o2[rr][d / 2].y * inv, o2[rr][d / 2 + 1].x * inv,
+                      o2[rr][d / 2 + 1].y * inv);
     }
     if (c == 0) {
-      M[row_idx] = m_i;
-      L[row_idx] = l_i;
+      M[row_idx[rr]] = m_i[rr];
+      L[row_idx[rr]] = l_i[rr];
     }
   }
 }
 
 template <typename T>
 int launch_typed(const StepArgs& a, cudaStream_t stream) {
-  const dim3 grid((a.Sq + kRows - 1) / kRows, a.H, a.B);
   const dim3 block(kThreads);
   const T* q = static_cast<const T*>(a.q);
   const T* k = static_cast<const T*>(a.k);
   const T* v = static_cast<const T*>(a.v);
 #define RAB_SIMT_CASE(DD)                                                                      \
-  case DD:                                                                                     \
+  case DD: {                                                                                   \
+    const dim3 grid((a.Sq + SimtCfg<DD>::kRows - 1) / SimtCfg<DD>::kRows, a.H, a.B);           \
     step_simt_kernel<T, DD><<<grid, block, 0, stream>>>(q, k, v, a.out, a.m, a.l, a.H, a.kvH,  \
                                                         a.Sq, a.Sk, a.kv_head_stride, a.qmap,  \
                                                         a.kmap, a.stride, a.flags, a.doc_len); \
-    break;
+    break;                                                                                     \
+  }
   switch (a.D) {
     RAB_SIMT_CASE(32)
     RAB_SIMT_CASE(64)
