@@ -86,20 +86,28 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.lines = []
+        self.t_mark = 0.0
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)],
+                                          "-lms", "10", "-i", str(self.index)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.perf_counter()  # the first sample takes nvidia-smi a moment: wait for it
+            while not self.lines and time.perf_counter() - t0 < 5.0:
+                time.sleep(0.01)
         except Exception:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def mark(self):
+        """Samples from here on are the ones taken during the timed regions."""
+        self.t_mark = time.perf_counter()
 
     def stop(self):
         if not self.proc:
@@ -111,7 +119,8 @@ class ClockSampler:
             pass
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        timed = [ln for t, ln in self.lines if t >= self.t_mark]
+        for ln in (timed if timed else [ln for _, ln in self.lines]):
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -282,6 +291,7 @@ def run_gpu_arm(args):
     K = max(1, args.steps)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     barrier()
+    sampler.mark()
     for i in range(K):
         flush.fill_(i & 1)  # evict L2 between timed iterations (not timed)
         if world > 1:
