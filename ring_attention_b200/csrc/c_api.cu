@@ -489,11 +489,15 @@ int ra_local_decode_step(const void* q, const ra_kv_cache* cache, int heads, int
   // workspace with room for both.
   float* ml = nullptr;
   RAB_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&ml), 2 * rows * sizeof(float), stream));
-  int rc = launch_init(out, ml, ml + rows, rows * cache->head_dim, rows, stream);
-  if (rc == RA_OK && cache->current_len > 0)
+  // init and the division by l ride on the fold of the split partials: two launches in all
+  int rc = RA_OK;
+  if (cache->current_len > 0) {
     rc = decode_step(cache->dtype, q, cache->k, cache->v, out, ml, ml + rows, s, q_pos_global,
-                     cache_k_offset, causal, stream, cache->s_max, nullptr, 0);
-  if (rc == RA_OK) rc = launch_finalize(out, ml + rows, rows, cache->head_dim, stream);
+                     cache_k_offset, causal, stream, cache->s_max, nullptr, 0,
+                     RA_STEP_FRESH | RA_STEP_FINALIZE);
+  } else {
+    rc = launch_init(out, ml, ml + rows, rows * cache->head_dim, rows, stream);
+  }
   cudaFreeAsync(ml, stream);
   return rc;
 }

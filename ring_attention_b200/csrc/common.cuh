@@ -120,7 +120,8 @@ bool step_stacked_supported(int dtype, int head_dim);
 // seq_q == 1 split-K decode step (decode.cu); workspace NULL = per-device buffer.
 int decode_step(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
                 float* l, const ra_shape& s, int q_offset, int k_offset, int causal,
-                cudaStream_t stream, int kv_row_stride, void* ws, size_t ws_bytes);
+                cudaStream_t stream, int kv_row_stride, void* ws, size_t ws_bytes,
+                unsigned flags = 0);  // RA_STEP_FRESH / RA_STEP_FINALIZE fused into the fold
 
 int launch_init(float* out, float* m, float* l, size_t out_count, size_t m_count,
                 cudaStream_t stream);

@@ -596,19 +596,33 @@ __global__ void __launch_bounds__(kMmaThreads)
 }
 
 // Fold n_split partials into the persistent (out, m, l). grid = (H, B), block = D threads.
+// RA_STEP_FRESH: the state is known to be empty (it is written, never read, which saves the
+// caller an init launch); RA_STEP_FINALIZE: divide by l after folding (saves the finalize
+// launch).
 __global__ void decode_reduce_kernel(const float* __restrict__ Mp, const float* __restrict__ Lp,
                                      const float* __restrict__ Op, float* __restrict__ M,
                                      float* __restrict__ L, float* __restrict__ O, int B, int H,
-                                     int D, int n_split) {
+                                     int D, int n_split, unsigned flags) {
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const size_t row = static_cast<size_t>(b) * H + h;
-  const float m_old = M[row];
+  const bool fresh = (flags & RA_STEP_FRESH) != 0, finalize = (flags & RA_STEP_FINALIZE) != 0;
+  const float m_old = fresh ? -INFINITY : M[row];
   float m_n = m_old;
   for (int s = 0; s < n_split; ++s) m_n = fmaxf(m_n, Mp[(static_cast<size_t>(s) * B + b) * H + h]);
-  if (m_n == -INFINITY) return;  // nothing visible anywhere: the state stays as it is
+  if (m_n == -INFINITY) {
+    // nothing visible anywhere: the state stays as it is (or is written empty)
+    if (fresh || finalize) {
+      O[row * D + d] = 0.f;
+      if (fresh && d == 0) {
+        M[row] = -INFINITY;
+        L[row] = 0.f;
+      }
+    }
+    return;
+  }
   const float a = (m_old == -INFINITY) ? 0.f : expf(m_old - m_n);
-  float o_acc = a * O[row * D + d];
-  float l_acc = a * L[row];
+  float o_acc = (m_old == -INFINITY) ? 0.f : a * O[row * D + d];
+  float l_acc = (m_old == -INFINITY) ? 0.f : a * L[row];
   for (int s = 0; s < n_split; ++s) {
     const size_t prow = (static_cast<size_t>(s) * B + b) * H + h;
     const float ms = Mp[prow];
@@ -616,6 +630,7 @@ __global__ void decode_reduce_kernel(const float* __restrict__ Mp, const float* 
     o_acc += sc * Op[prow * D + d];
     l_acc += sc * Lp[prow];
   }
+  if (finalize) o_acc *= l_acc > 0.f ? 1.f / l_acc : 0.f;
   O[row * D + d] = o_acc;
   __syncthreads();  // every thread has read M/L before thread 0 overwrites them
   if (d == 0) {
@@ -686,7 +701,7 @@ template <typename T, int D>
 int launch_decode_typed(const void* q, const void* k, const void* v, float* out, float* m,
                         float* l, const ra_shape& s, int sk_eff, long long kv_head_stride,
                         void* workspace, size_t workspace_bytes, cudaStream_t stream,
-                        int split_cap = kMaxSplits) {
+                        int split_cap = kMaxSplits, unsigned flags = 0) {
   if constexpr (sizeof(T) == 2 && D >= 64) {
     // 16-bit caches: the tensor-core kernel (16 query heads per block, 64-key stages)
     using M = MmaCfg<D>;
@@ -723,7 +738,7 @@ int launch_decode_typed(const void* q, const void* k, const void* v, float* out,
         s.batch, s.heads, kvH, sk_eff, kv_head_stride, rps, head_batches, scale_log2);
     RAB_CUDA(cudaGetLastError());
     decode_reduce_kernel<<<dim3(s.heads, s.batch), D, 0, stream>>>(Mp, Lp, Op, m, l, out, s.batch,
-                                                                   s.heads, D, n_split);
+                                                                   s.heads, D, n_split, flags);
     RAB_CUDA(cudaGetLastError());
     return RA_OK;
   }
@@ -766,7 +781,7 @@ int launch_decode_typed(const void* q, const void* k, const void* v, float* out,
 #undef RAB_DECODE_GB
   RAB_CUDA(cudaGetLastError());
   decode_reduce_kernel<<<dim3(s.heads, s.batch), D, 0, stream>>>(Mp, Lp, Op, m, l, out, s.batch,
-                                                                 s.heads, D, p.n_split);
+                                                                 s.heads, D, p.n_split, flags);
   RAB_CUDA(cudaGetLastError());
   return RA_OK;
 }
@@ -775,20 +790,20 @@ template <typename T>
 int launch_decode_dtype(const void* q, const void* k, const void* v, float* out, float* m,
                         float* l, const ra_shape& s, int sk_eff, long long kv_head_stride,
                         void* ws, size_t ws_bytes, cudaStream_t stream,
-                        int split_cap = kMaxSplits) {
+                        int split_cap = kMaxSplits, unsigned flags = 0) {
   switch (s.head_dim) {
     case 32:
       return launch_decode_typed<T, 32>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                        ws_bytes, stream, split_cap);
+                                        ws_bytes, stream, split_cap, flags);
     case 64:
       return launch_decode_typed<T, 64>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                        ws_bytes, stream, split_cap);
+                                        ws_bytes, stream, split_cap, flags);
     case 128:
       return launch_decode_typed<T, 128>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                         ws_bytes, stream, split_cap);
+                                         ws_bytes, stream, split_cap, flags);
     case 256:
       return launch_decode_typed<T, 256>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                         ws_bytes, stream, split_cap);
+                                         ws_bytes, stream, split_cap, flags);
   }
   set_error("attention_decode_step: unsupported head_dim=%d (supported: 32, 64, 128, 256)",
             s.head_dim);
@@ -799,7 +814,8 @@ int launch_decode_dtype(const void* q, const void* k, const void* v, float* out,
 
 int decode_step(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
                 float* l, const ra_shape& s, int q_offset, int k_offset, int causal,
-                cudaStream_t stream, int kv_row_stride, void* ws, size_t ws_bytes) {
+                cudaStream_t stream, int kv_row_stride, void* ws, size_t ws_bytes,
+                unsigned flags) {
   RAB_REQUIRE(q && k && v && out && m && l, RA_ERR_INVALID, "decode step: null argument");
   RAB_REQUIRE(s.seq_q == 1, RA_ERR_INVALID, "decode step: seq_q must be 1 (got %d)", s.seq_q);
   RAB_REQUIRE(s.batch > 0 && s.heads > 0 && s.batch <= 65535, RA_ERR_INVALID,
@@ -813,19 +829,25 @@ int decode_step(int dtype, const void* q, const void* k, const void* v, float* o
     const long long vis = static_cast<long long>(q_offset) - k_offset + 1;
     if (vis < sk_eff) sk_eff = vis < 0 ? 0 : static_cast<int>(vis);
   }
-  if (sk_eff <= 0) return RA_OK;  // nothing visible: the state stays as it is
+  if (sk_eff <= 0) {
+    // nothing visible: the state stays as it is, or is written empty / normalised on request
+    const size_t rows = static_cast<size_t>(s.batch) * s.heads;
+    if (flags & RA_STEP_FRESH) return launch_init(out, m, l, rows * s.head_dim, rows, stream);
+    if (flags & RA_STEP_FINALIZE) return launch_finalize(out, l, rows, s.head_dim, stream);
+    return RA_OK;
+  }
   const int stride_rows = kv_row_stride > 0 ? kv_row_stride : s.seq_k;
   const long long kv_head_stride = static_cast<long long>(stride_rows) * s.head_dim;
   switch (dtype) {
     case RA_F32:
       return launch_decode_dtype<float>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                        ws_bytes, stream);
+                                        ws_bytes, stream, kMaxSplits, flags);
     case RA_F16:
       return launch_decode_dtype<__half>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                         ws_bytes, stream);
+                                         ws_bytes, stream, kMaxSplits, flags);
     case RA_BF16:
       return launch_decode_dtype<__nv_bfloat16>(q, k, v, out, m, l, s, sk_eff, kv_head_stride, ws,
-                                                ws_bytes, stream);
+                                                ws_bytes, stream, kMaxSplits, flags);
   }
   set_error("decode step: unknown dtype %d", dtype);
   return RA_ERR_INVALID;

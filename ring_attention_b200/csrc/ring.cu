@@ -528,15 +528,17 @@ int ra_ring_decode_step_raw(ra_ring* r, int dtype, int batch, int heads, int kv_
   float* m_p = send + bh * D;
   float* l_p = m_p + bh;
   RAB_CUDA(cudaEventRecord(r->ev_start, stream));
-  int rc = launch_init(o_p, m_p, l_p, bh * D, bh, stream);
-  if (rc != RA_OK) return rc;
+  int rc = RA_OK;
   if (local_len > 0) {
     ra_shape s{batch, heads, 1, local_len, D, kv_heads};
-    // causality is implicit: the cache only ever holds past tokens (src/ring_decode.cu:173-175)
+    // causality is implicit: the cache only ever holds past tokens (src/ring_decode.cu:173-175);
+    // the partial is written into the empty send block by the fold itself (no init launch)
     rc = decode_step(dtype, q, k_cache, v_cache, o_p, m_p, l_p, s, 0, 0, 0, stream, s_max, nullptr,
-                     0);
-    if (rc != RA_OK) return rc;
+                     0, RA_STEP_FRESH);
+  } else {
+    rc = launch_init(o_p, m_p, l_p, bh * D, bh, stream);
   }
+  if (rc != RA_OK) return rc;
   RAB_CUDA(cudaEventRecord(r->ev_comp[0], stream));
   const float* gathered = send;
   if (r->cp > 1) {
