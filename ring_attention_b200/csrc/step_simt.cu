@@ -13,8 +13,10 @@
 // the head dimension each, 8 at head_dim 32) and every thread carries TWO rows, so a K or V
 // value read from shared memory feeds two multiply-adds and the inner loops are bound by the
 // FMA pipe (packed fp32x2 multiply-adds) instead of by shared-memory reads. K/V tiles of
-// 4096/D keys are staged in shared memory as fp32; a score is a partial dot product per thread
-// plus a shuffle reduction over the row's threads.
+// 8192/D keys are staged in shared memory as fp32; a score is a partial dot product per thread
+// plus a transposing shuffle reduction over the row's threads, which leaves each complete
+// score on exactly one lane: that lane masks and exponentiates it, and the weights travel back
+// by shuffle for the second product.
 #include <cfloat>
 
 #include "common.cuh"
@@ -33,7 +35,8 @@ struct SimtCfg {
   static constexpr int kDQ = D / kTPR;               // head-dimension elements per thread
   static constexpr int kGroups = kThreads / kTPR;    // row groups per block
   static constexpr int kRows = kGroups * kR;         // query rows per block
-  static constexpr int kBC = 4096 / D;               // keys per shared-memory tile
+  static constexpr int kBC = 8192 / D;               // keys per shared-memory tile (32 KiB each of K, V)
+  static constexpr int kSmemBytes = 2 * kBC * D * 4 + kBC * 4;
 };
 
 // packed fp32x2 multiply-add: one instruction for two lanes
@@ -95,12 +98,16 @@ __global__ void __launch_bounds__(kThreads, 2)
                      int stride, unsigned flags, long long doc_len) {
   using C = SimtCfg<D>;
   constexpr int DQ = C::kDQ, BC = C::kBC, TPR = C::kTPR;
-  static_assert(BC % kChunk == 0, "tile must be a whole number of chunks");
+  constexpr int CH = kChunk > TPR ? kChunk : TPR;  // keys folded per online-softmax update
+  constexpr int KPL = CH / TPR;                    // of which this lane scores KPL
+  static_assert(BC % CH == 0, "tile must be a whole number of chunks");
   static_assert(DQ % 4 == 0, "float4 loads");
-  __shared__ __align__(16) float Ks[BC * D];
-  __shared__ __align__(16) float Vs[BC * D];
-  __shared__ int kpos_s[BC];
+  extern __shared__ __align__(16) unsigned char simt_smem[];
+  float* Ks = reinterpret_cast<float*>(simt_smem);
+  float* Vs = Ks + BC * D;
+  int* kpos_s = reinterpret_cast<int*>(Vs + BC * D);
   __shared__ int qmax_s;
+  static_assert(BC <= kThreads, "one thread per key computes the tile's positions");
 
   const bool causal = (flags & RA_STEP_CAUSAL) != 0;
   const bool fresh = (flags & RA_STEP_FRESH) != 0;
@@ -155,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           o2[rr][d / 2 + 1] = make_float2(x.z, x.w);
         }
         m_i[rr] = M[row_idx[rr]];
-        l_i[rr] = L[row_idx[rr]];
+        l_i[rr] = c == 0 ? L[row_idx[rr]] : 0.f;  // the row sum is kept as per-lane shares
       }
     }
   }
@@ -192,75 +199,95 @@ __global__ void __launch_bounds__(kThreads, 2)
     __syncthreads();
 
 #pragma unroll 1
-    for (int jc = 0; jc < BC; jc += kChunk) {
-      float s[kR][kChunk];
+    for (int jc = 0; jc < BC; jc += CH) {
+      // Scores of CH keys for both rows. The partial dot products of a group of TPR keys are
+      // summed with a transposing reduction (TPR - 1 shuffles per group and row): afterwards
+      // lane c of the row holds the complete score of key c of the group, so the mask, the
+      // maximum and the exponential of a key are computed once, not once per lane.
+      float sc[kR][KPL];  // this lane's keys: group gi, key gi * TPR + c of the chunk
 #pragma unroll
-      for (int jj = 0; jj < kChunk; ++jj) {
-        const float* kr = &Ks[(jc + jj) * D + c * DQ];
-        float2 acc[kR];
+      for (int gi = 0; gi < KPL; ++gi) {
+        float part[kR][TPR];
 #pragma unroll
-        for (int rr = 0; rr < kR; ++rr) acc[rr] = make_float2(0.f, 0.f);
+        for (int t = 0; t < TPR; ++t) {
+          const float* kr = &Ks[(jc + gi * TPR + t) * D + c * DQ];
+          float2 acc[kR];
 #pragma unroll
-        for (int d = 0; d < DQ; d += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
-          const float2 ka = make_float2(k4.x, k4.y), kb = make_float2(k4.z, k4.w);
+          for (int rr = 0; rr < kR; ++rr) acc[rr] = make_float2(0.f, 0.f);
 #pragma unroll
-          for (int rr = 0; rr < kR; ++rr) {
-            acc[rr] = ffma2(q2[rr][d / 2], ka, acc[rr]);
-            acc[rr] = ffma2(q2[rr][d / 2 + 1], kb, acc[rr]);
+          for (int d = 0; d < DQ; d += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
+            const float2 ka = make_float2(k4.x, k4.y), kb = make_float2(k4.z, k4.w);
+#pragma unroll
+            for (int rr = 0; rr < kR; ++rr) {
+              acc[rr] = ffma2(q2[rr][d / 2], ka, acc[rr]);
+              acc[rr] = ffma2(q2[rr][d / 2 + 1], kb, acc[rr]);
+            }
           }
+#pragma unroll
+          for (int rr = 0; rr < kR; ++rr) part[rr][t] = acc[rr].x + acc[rr].y;
         }
 #pragma unroll
         for (int rr = 0; rr < kR; ++rr) {
-          float a = acc[rr].x + acc[rr].y;
 #pragma unroll
-          for (int o = 1; o < TPR; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-          s[rr][jj] = a;
+          for (int o = TPR / 2; o >= 1; o >>= 1) {
+            const bool upper = (c & o) != 0;  // this lane keeps the upper half of the values
+#pragma unroll
+            for (int t = 0; t < o; ++t) {
+              const float keep = upper ? part[rr][t + o] : part[rr][t];
+              const float send = upper ? part[rr][t] : part[rr][t + o];
+              part[rr][t] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+            }
+          }
+          sc[rr][gi] = part[rr][0];
         }
       }
-      float alpha[kR];
       bool live[kR];
 #pragma unroll
       for (int rr = 0; rr < kR; ++rr) {
-        float m_new = m_i[rr];
+        float m_new = -INFINITY;
 #pragma unroll
-        for (int jj = 0; jj < kChunk; ++jj) {
-          const int kp = kpos_s[jc + jj];
+        for (int gi = 0; gi < KPL; ++gi) {
+          const int kp = kpos_s[jc + gi * TPR + c];
           bool vis = (kp != INT_MAX) && (!causal || kp <= qpos[rr]);
           if (doc_len > 0 && vis) vis = (kp / doc_len) == qdoc[rr];
-          if (vis) {
-            s[rr][jj] *= scale;
-            m_new = fmaxf(m_new, s[rr][jj]);
-          } else {
-            s[rr][jj] = -INFINITY;
-          }
+          sc[rr][gi] = vis ? sc[rr][gi] * scale : -INFINITY;
+          m_new = fmaxf(m_new, sc[rr][gi]);
         }
-        live[rr] = m_new != -INFINITY;  // false: nothing visible so far, state unchanged
-        alpha[rr] = live[rr] ? expf(m_i[rr] - m_new) : 1.f;
-        float row_sum = 0.f;
 #pragma unroll
-        for (int jj = 0; jj < kChunk; ++jj) {
-          s[rr][jj] = (s[rr][jj] == -INFINITY) ? 0.f : expf(s[rr][jj] - m_new);
-          row_sum += s[rr][jj];
+        for (int o = 1; o < TPR; o <<= 1) m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, o));
+        m_new = fmaxf(m_new, m_i[rr]);
+        live[rr] = m_new != -INFINITY;  // false: nothing visible so far, state unchanged
+        const float alpha = live[rr] ? expf(m_i[rr] - m_new) : 1.f;
+        float part_sum = 0.f;
+#pragma unroll
+        for (int gi = 0; gi < KPL; ++gi) {
+          sc[rr][gi] = (sc[rr][gi] == -INFINITY) ? 0.f : expf(sc[rr][gi] - m_new);
+          part_sum += sc[rr][gi];
         }
         if (live[rr]) {
-          l_i[rr] = alpha[rr] * l_i[rr] + row_sum;
+          l_i[rr] = alpha * l_i[rr] + part_sum;  // per-lane share of the row sum
           m_i[rr] = m_new;
-          const float2 a2 = make_float2(alpha[rr], alpha[rr]);
 #pragma unroll
-          for (int d = 0; d < DQ / 2; ++d) o2[rr][d] = make_float2(o2[rr][d].x * a2.x, o2[rr][d].y * a2.y);
+          for (int d = 0; d < DQ / 2; ++d)
+            o2[rr][d] = make_float2(o2[rr][d].x * alpha, o2[rr][d].y * alpha);
         }
       }
       bool any_live = false;
 #pragma unroll
       for (int rr = 0; rr < kR; ++rr) any_live |= live[rr];
-      if (!any_live) continue;
+      // the weights are fetched from their owner lanes with warp shuffles below, so the whole
+      // warp takes this branch together
+      if (!__any_sync(0xffffffffu, any_live)) continue;
 #pragma unroll
-      for (int jj = 0; jj < kChunk; ++jj) {
+      for (int jj = 0; jj < CH; ++jj) {
         const float* vr = &Vs[(jc + jj) * D + c * DQ];
         float2 p2[kR];
 #pragma unroll
-        for (int rr = 0; rr < kR; ++rr) p2[rr] = make_float2(s[rr][jj], s[rr][jj]);
+        for (int rr = 0; rr < kR; ++rr) {
+          const float pw = __shfl_sync(0xffffffffu, sc[rr][jj / TPR], jj % TPR, TPR);
+          p2[rr] = make_float2(pw, pw);
+        }
 #pragma unroll
         for (int d = 0; d < DQ; d += 4) {
           const float4 v4 = *reinterpret_cast<const float4*>(vr + d);
@@ -276,6 +303,11 @@ __global__ void __launch_bounds__(kThreads, 2)
     __syncthreads();  // everyone is done with Ks/Vs/kpos_s before the next tile overwrites them
   }
 
+#pragma unroll
+  for (int rr = 0; rr < kR; ++rr) {
+#pragma unroll
+    for (int o = 1; o < TPR; o <<= 1) l_i[rr] += __shfl_xor_sync(0xffffffffu, l_i[rr], o);
+  }
 #pragma unroll
   for (int rr = 0; rr < kR; ++rr) {
     if (!active[rr]) continue;
@@ -304,9 +336,12 @@ int launch_typed(const StepArgs& a, cudaStream_t stream) {
 #define RAB_SIMT_CASE(DD)                                                                      \
   case DD: {                                                                                   \
     const dim3 grid((a.Sq + SimtCfg<DD>::kRows - 1) / SimtCfg<DD>::kRows, a.H, a.B);           \
-    step_simt_kernel<T, DD><<<grid, block, 0, stream>>>(q, k, v, a.out, a.m, a.l, a.H, a.kvH,  \
-                                                        a.Sq, a.Sk, a.kv_head_stride, a.qmap,  \
-                                                        a.kmap, a.stride, a.flags, a.doc_len); \
+    RAB_CUDA(cudaFuncSetAttribute(step_simt_kernel<T, DD>,                                     \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
+                                  SimtCfg<DD>::kSmemBytes));                                   \
+    step_simt_kernel<T, DD><<<grid, block, SimtCfg<DD>::kSmemBytes, stream>>>(                 \
+        q, k, v, a.out, a.m, a.l, a.H, a.kvH, a.Sq, a.Sk, a.kv_head_stride, a.qmap, a.kmap,    \
+        a.stride, a.flags, a.doc_len);                                                         \
     break;                                                                                     \
   }
   switch (a.D) {
