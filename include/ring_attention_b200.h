@@ -94,7 +94,8 @@ RA_API int ra_attention_step(const float* q, const float* k, const float* v, flo
 
 /* One ring step, fp16 Q/K/V, fp32 state. Replaces launch_attention_step_fp16
  * (src/attention.hpp:147-150, src/attention_step_fp16.cu:256-326). Runs the tcgen05 kernel
- * for head_dim 64 and 128 and the SIMT kernel for 32 and 256. */
+ * for head_dim 32, 64 and 128 (32 on the 64-wide kernel, the loads zero-filling the upper half
+ * of every row) and the SIMT kernel for 256. */
 RA_API int ra_attention_step_fp16(const void* q, const void* k, const void* v, float* out,
                                   float* m, float* l, const ra_shape* shape, int q_offset,
                                   int k_offset, int causal, ra_stream stream, int pos_stride);
@@ -129,7 +130,7 @@ RA_API int ra_attention_step_ex(int dtype, const void* q, const void* k, const v
  * starts s * batch * kv_heads * shard_rows * head_dim elements later (the receive buffer of an
  * all-gather of per-rank shards). Key segment i of kmap is rows seg_row[i] .. seg_row[i] +
  * seg_len of shard seg_shard[i]; shape->seq_k = kmap->n_seg * kmap->seg_len. 16-bit dtypes and
- * head_dim 64 / 128 only (RA_ERR_INVALID otherwise). One launch then folds the shards of
+ * head_dim 32 / 64 / 128 only (RA_ERR_INVALID otherwise). One launch then folds the shards of
  * several ring steps; the reference has no counterpart (its all-gather mode copies the shards
  * into one tensor first, src/ring_loop.cu:273-420). */
 RA_API int ra_attention_step_stacked(int dtype, const void* q, const void* k, const void* v,

@@ -79,7 +79,7 @@ int step_ex(int dtype, const void* q, const void* k, const void* v, float* out, 
 }  // namespace
 
 bool step_stacked_supported(int dtype, int head_dim) {
-  return (dtype == RA_F16 || dtype == RA_BF16) && (head_dim == 64 || head_dim == 128);
+  return (dtype == RA_F16 || dtype == RA_BF16) && (head_dim == 32 || head_dim == 64 || head_dim == 128);
 }
 
 int step_stacked(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
@@ -89,7 +89,7 @@ int step_stacked(int dtype, const void* q, const void* k, const void* v, float* 
   RAB_REQUIRE(q && k && v && out && m && l && seg_shard && seg_row, RA_ERR_INVALID,
               "stacked step: null argument");
   RAB_REQUIRE(step_stacked_supported(dtype, s.head_dim), RA_ERR_INVALID,
-              "stacked step: needs a 16-bit dtype and head_dim 64 or 128");
+              "stacked step: needs a 16-bit dtype and head_dim 32, 64 or 128");
   RAB_REQUIRE(kmap.n_seg >= 1 && kmap.n_seg <= RA_MAX_SEG && kmap.seg_len >= 1 &&
                   kmap.n_seg * kmap.seg_len == s.seq_k && n_shards >= 1 && shard_rows >= 1,
               RA_ERR_INVALID, "stacked step: bad key map");

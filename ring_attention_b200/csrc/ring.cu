@@ -249,7 +249,7 @@ static bool use_gather(const ra_ring* r, const ra_ring_config* c, size_t kv_raw)
 // not fill the GPU twice over: a block's loop over every gathered key is then the critical
 // path of the pass, and splitting the keys shortens it.
 struct GatherPlan {
-  bool stacked;        // false: one plain step per shard (fp32, head_dim 32 / 256)
+  bool stacked;        // false: one plain step per shard (fp32, head_dim 256)
   int nsg;             // key segments per shard
   int entries;         // (cp - 1) * nsg
   int parts;           // launches over the entries

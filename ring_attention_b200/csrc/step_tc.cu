@@ -403,6 +403,7 @@ struct TcArgs {
   float* m;
   float* l;
   int H, kvH, Sq;
+  int d_real;  // head_dim of the tensors in memory (32 runs on the 64-wide kernel, see launch_cfg)
   int n_qblocks_per_seg;
   PosMap qmap, kmap;
   int kseg_head[RA_MAX_SEG];  // key segment -> head-coordinate offset and first row in K / V
@@ -672,7 +673,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool row_valid = r_in_seg < q_seg_len;
     const int qpos = a.qmap.base[sq] + r_in_seg * a.stride;
     const long long qdoc = a.doc_len > 0 ? qpos / a.doc_len : 0;
-    const float scale_log2 = rsqrtf(static_cast<float>(D)) * kLog2e;
+    const float scale_log2 = rsqrtf(static_cast<float>(a.d_real)) * kLog2e;
 
     float m_used = -INFINITY;  // reference point of P and O, log2 units
     float m_true = -INFINITY;  // true running max, log2 units
@@ -859,7 +860,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const size_t grow = (static_cast<size_t>(bh) * a.Sq + static_cast<size_t>(sq) * q_seg_len +
                            (row_valid ? r_in_seg : 0));
-      float* o_g = a.out + grow * D;
+      float* o_g = a.out + grow * a.d_real;
       // (the polynomial exponential turns a hidden score into 2^-125, not 0, so "saw a key"
       // is read off the running maximum, not off the sum)
       const bool have = row_valid && n_tiles > 0 && m_true > -INFINITY;
@@ -878,7 +879,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       // a row that saw nothing keeps its state unless the caller asked to overwrite / normalise
       const bool touch = row_valid && (have || fresh || finalize);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < a.d_real / 32; ++c) {
         float o[32];
         if (n_tiles > 0) {  // block-uniform: the tensor-memory load is warp-collective
           tmem_ld32(t_o + c * 32, o);
@@ -944,7 +945,9 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// (D, rows, heads) 16-bit tensor, box = 64 elements x 128 rows x 1, 128B swizzle.
+// (D, rows, heads) 16-bit tensor, box = 64 elements x 128 rows x 1, 128B swizzle. With D = 32
+// the box is wider than the tensor: the upper 32 elements of every row are out of bounds and
+// arrive as zeros, which is exactly a head_dim 64 tile whose upper half is zero.
 int make_map(CUtensorMap* map, int dtype, const void* base, int D, long long rows,
              long long heads, long long head_stride_elems) {
   EncodeTiledFn fn = encode_fn();
@@ -972,12 +975,12 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   using C = TcCfg<D, kPInTmem>;
   CUtensorMap mq, mk, mv;
   const int dtype = kBf16 ? RA_BF16 : RA_F16;
-  int rc = make_map(&mq, dtype, a.q, D, a.Sq, static_cast<long long>(a.B) * a.H,
-                    static_cast<long long>(a.Sq) * D);
+  int rc = make_map(&mq, dtype, a.q, a.D, a.Sq, static_cast<long long>(a.B) * a.H,
+                    static_cast<long long>(a.Sq) * a.D);
   if (rc != RA_OK) return rc;
-  rc = make_map(&mk, dtype, a.k, D, a.k_rows, a.k_heads_total, a.kv_head_stride);
+  rc = make_map(&mk, dtype, a.k, a.D, a.k_rows, a.k_heads_total, a.kv_head_stride);
   if (rc != RA_OK) return rc;
-  rc = make_map(&mv, dtype, a.v, D, a.k_rows, a.k_heads_total, a.kv_head_stride);
+  rc = make_map(&mv, dtype, a.v, a.D, a.k_rows, a.k_heads_total, a.kv_head_stride);
   if (rc != RA_OK) return rc;
 
   TcArgs t;
@@ -987,6 +990,7 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.H = a.H;
   t.kvH = a.kvH;
   t.Sq = a.Sq;
+  t.d_real = a.D;
   t.n_qblocks_per_seg = (a.qmap.seg_len + kQBlock - 1) / kQBlock;
   t.qmap = a.qmap;
   t.kmap = a.kmap;
@@ -1021,7 +1025,7 @@ int launch_d(int dtype, const StepArgs& a, cudaStream_t stream) {
 
 bool step_tc_supported(int dtype, const StepArgs& a) {
   if (dtype != RA_F16 && dtype != RA_BF16) return false;
-  if (a.D != 64 && a.D != 128) return false;
+  if (a.D != 32 && a.D != 64 && a.D != 128) return false;
   if (a.Sq <= 0 || a.Sk <= 0) return false;
   if (a.qmap.n_seg * a.qmap.seg_len != a.Sq || a.kmap.n_seg * a.kmap.seg_len != a.Sk) return false;
   if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
@@ -1032,7 +1036,9 @@ bool step_tc_supported(int dtype, const StepArgs& a) {
 
 int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream) {
   RAB_REQUIRE(a.status != nullptr, RA_ERR_CUDA, "attention step: no device status word");
-  if (a.D == 64) return launch_d<64>(dtype, a, stream);
+  // head_dim 32 runs on the 64-wide kernel: the loads zero-fill the upper half of every row
+  // (see make_map), so the scores are exact and the upper 32 output columns are never stored
+  if (a.D == 32 || a.D == 64) return launch_d<64>(dtype, a, stream);
   return launch_d<128>(dtype, a, stream);
 }
 

@@ -137,7 +137,7 @@ def positions(sm, stride):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("D", [32, 64, 128])
 @pytest.mark.parametrize("simt", [False, True])
 def test_segmented_zigzag_step_all_paths(dtype, D, simt):
     # rank 1 of 4, zig-zag with 4 sub-groups, ring step 2: q and k segments at scattered bases
@@ -338,7 +338,7 @@ def test_unsupported_head_dim_is_an_error_not_a_crash():
     assert "unsupported head_dim=48" in str(e.value)
 
 
-@pytest.mark.parametrize("dtype,D", [(torch.float16, 64), (torch.bfloat16, 128)])
+@pytest.mark.parametrize("dtype,D", [(torch.float16, 64), (torch.bfloat16, 128), (torch.float16, 32)])
 @pytest.mark.parametrize("layout,ns,chunk", [(1, 2, 48), (1, 4, 128), (2, 1, 200), (0, 1, 320)])
 def test_stacked_shards_fold_several_ring_steps_in_one_launch(dtype, D, layout, ns, chunk):
     """The gather schedule on one GPU: every rank's K/V shard stacked as an all-gather leaves
@@ -378,14 +378,14 @@ def test_stacked_shards_fold_several_ring_steps_in_one_launch(dtype, D, layout, 
 
 
 def test_stacked_step_rejects_what_the_tensor_core_kernel_cannot_read():
-    q = torch.zeros((1, 1, 64, 32), device="cuda", dtype=torch.float16)
-    ks = torch.zeros((2, 1, 1, 64, 32), device="cuda", dtype=torch.float16)
-    out, m, l = state(1, 1, 64, 32)
+    q = torch.zeros((1, 1, 64, 256), device="cuda", dtype=torch.float16)
+    ks = torch.zeros((2, 1, 1, 64, 256), device="cuda", dtype=torch.float16)
+    out, m, l = state(1, 1, 64, 256)
     qm, km = SegMap(), SegMap()
     qm.n_seg, qm.seg_len = 1, 64
     km.n_seg, km.seg_len = 2, 64
-    with pytest.raises(RuntimeError):
-        api.attention_step_stacked(q, ks, ks, out, m, l, api.AttentionShape(1, 1, 64, 128, 32, 1), qm, km,
+    with pytest.raises(RuntimeError):  # head_dim 256 has no tensor-core kernel
+        api.attention_step_stacked(q, ks, ks, out, m, l, api.AttentionShape(1, 1, 64, 128, 256, 1), qm, km,
                                    [0, 1], [0, 0])
     q64 = torch.zeros((1, 1, 64, 64), device="cuda", dtype=torch.float16)
     ks64 = torch.zeros((2, 1, 1, 64, 64), device="cuda", dtype=torch.float16)
