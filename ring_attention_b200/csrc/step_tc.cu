@@ -403,7 +403,6 @@ struct TcArgs {
   float* m;
   float* l;
   int H, kvH, Sq;
-  int d_real;  // head_dim of the tensors in memory (32 runs on the 64-wide kernel, see launch_cfg)
   int n_qblocks_per_seg;
   PosMap qmap, kmap;
   int kseg_head[RA_MAX_SEG];  // key segment -> head-coordinate offset and first row in K / V
@@ -414,7 +413,8 @@ struct TcArgs {
   int* status;
 };
 
-template <int D, bool kBf16, bool kPInTmem>
+// DR is the head_dim of the tensors in memory: D, or 32 on the 64-wide kernel (see launch_cfg).
+template <int D, bool kBf16, bool kPInTmem, int DR>
 __global__ void __launch_bounds__(kThreads, 1)
     step_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k,
@@ -673,7 +673,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool row_valid = r_in_seg < q_seg_len;
     const int qpos = a.qmap.base[sq] + r_in_seg * a.stride;
     const long long qdoc = a.doc_len > 0 ? qpos / a.doc_len : 0;
-    const float scale_log2 = rsqrtf(static_cast<float>(a.d_real)) * kLog2e;
+    const float scale_log2 = rsqrtf(static_cast<float>(DR)) * kLog2e;
 
     float m_used = -INFINITY;  // reference point of P and O, log2 units
     float m_true = -INFINITY;  // true running max, log2 units
@@ -860,7 +860,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const size_t grow = (static_cast<size_t>(bh) * a.Sq + static_cast<size_t>(sq) * q_seg_len +
                            (row_valid ? r_in_seg : 0));
-      float* o_g = a.out + grow * a.d_real;
+      float* o_g = a.out + grow * DR;
       // (the polynomial exponential turns a hidden score into 2^-125, not 0, so "saw a key"
       // is read off the running maximum, not off the sum)
       const bool have = row_valid && n_tiles > 0 && m_true > -INFINITY;
@@ -879,7 +879,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       // a row that saw nothing keeps its state unless the caller asked to overwrite / normalise
       const bool touch = row_valid && (have || fresh || finalize);
 #pragma unroll 1
-      for (int c = 0; c < a.d_real / 32; ++c) {
+      for (int c = 0; c < DR / 32; ++c) {
         float o[32];
         if (n_tiles > 0) {  // block-uniform: the tensor-memory load is warp-collective
           tmem_ld32(t_o + c * 32, o);
@@ -970,7 +970,7 @@ int make_map(CUtensorMap* map, int dtype, const void* base, int D, long long row
 
 int g_p_in_tmem = 1;  // which P path the launcher uses (both are kept buildable and tested)
 
-template <int D, bool kBf16, bool kPInTmem>
+template <int D, bool kBf16, bool kPInTmem, int DR>
 int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   using C = TcCfg<D, kPInTmem>;
   CUtensorMap mq, mk, mv;
@@ -990,7 +990,6 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.H = a.H;
   t.kvH = a.kvH;
   t.Sq = a.Sq;
-  t.d_real = a.D;
   t.n_qblocks_per_seg = (a.qmap.seg_len + kQBlock - 1) / kQBlock;
   t.qmap = a.qmap;
   t.kmap = a.kmap;
@@ -1005,7 +1004,7 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   const long long n_qblocks = static_cast<long long>(t.n_qblocks_per_seg) * a.qmap.n_seg;
   RAB_REQUIRE(n_qblocks <= 65535, RA_ERR_INVALID, "attention step: too many query blocks (%lld)",
               n_qblocks);
-  auto kern = step_tc_kernel<D, kBf16, kPInTmem>;
+  auto kern = step_tc_kernel<D, kBf16, kPInTmem, DR>;
   RAB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   const dim3 grid(static_cast<unsigned>(a.B) * a.H, static_cast<unsigned>(n_qblocks));
   kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, t);
@@ -1015,10 +1014,20 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
 
 template <int D>
 int launch_d(int dtype, const StepArgs& a, cudaStream_t stream) {
-  if (dtype == RA_BF16) {
-    return g_p_in_tmem ? launch_cfg<D, true, true>(a, stream) : launch_cfg<D, true, false>(a, stream);
+  // the 64-wide kernel also takes head_dim 32 (DR = 32)
+  if constexpr (D == 64) {
+    if (a.D == 32) {
+      if (dtype == RA_BF16)
+        return g_p_in_tmem ? launch_cfg<64, true, true, 32>(a, stream)
+                           : launch_cfg<64, true, false, 32>(a, stream);
+      return g_p_in_tmem ? launch_cfg<64, false, true, 32>(a, stream)
+                         : launch_cfg<64, false, false, 32>(a, stream);
+    }
   }
-  return g_p_in_tmem ? launch_cfg<D, false, true>(a, stream) : launch_cfg<D, false, false>(a, stream);
+  if (dtype == RA_BF16) {
+    return g_p_in_tmem ? launch_cfg<D, true, true, D>(a, stream) : launch_cfg<D, true, false, D>(a, stream);
+  }
+  return g_p_in_tmem ? launch_cfg<D, false, true, D>(a, stream) : launch_cfg<D, false, false, D>(a, stream);
 }
 
 }  // namespace
