@@ -277,6 +277,16 @@ RA_API int ra_ring2d_source(int num_nodes, int gpus_per_node, int node, int loca
 RA_API int ra_ring_step_maps(int cp_size, int rank, int seq, int mode, int n_splits, int step,
                              ra_segmap* qmap, ra_segmap* kmap);
 
+/* Gather schedule, host only: the key segments of the other cp_size - 1 ranks' shards that part
+ * `part` of `parts` folds for `rank` (entry e = (s - 1) * n_sub_groups + i is sub-group i of the
+ * shard s hops away; part z takes e = z, z + parts, ...). Fills kmap (one base per segment) and,
+ * per segment, the owning rank (= shard index in the gathered buffer) and the first row inside
+ * that shard. Returns the position stride, or -1 on bad arguments or more than RA_MAX_SEG
+ * segments. Over all parts, plus the rank's own shard, every key of the sequence appears once. */
+RA_API int ra_ring_gather_part_maps(int cp_size, int rank, int seq, int mode, int n_splits,
+                                    int parts, int part, ra_segmap* kmap, int* seg_shard,
+                                    int* seg_row);
+
 /* Causal-adjusted work of one rank at one ring step, in (query, key) pairs that are
  * visible (the FLOP model of apps/bench_attention/bench_attention.cu:46-51 is
  * 4 * head_dim * heads * batch * pairs). Host only; exact, O(n_seg^2). */

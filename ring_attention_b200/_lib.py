@@ -121,6 +121,8 @@ _SIG = {
     "ra_partition_next_rank": (C.c_int, [C.c_int] * 2),
     "ra_partition_prev_rank": (C.c_int, [C.c_int] * 2),
     "ra_ring2d_source": (C.c_int, [C.c_int] * 6),
+    "ra_ring_gather_part_maps": (C.c_int, [C.c_int] * 7 + [C.POINTER(SegMap), C.POINTER(C.c_int),
+                                                     C.POINTER(C.c_int)]),
     "ra_ring_step_maps": (C.c_int, [C.c_int] * 6 + [C.POINTER(SegMap), C.POINTER(SegMap)]),
     "ra_ring_step_visible_pairs": (C.c_double, [C.POINTER(SegMap), C.POINTER(SegMap), C.c_int,
                                                 C.c_int, C.c_longlong]),

@@ -558,6 +558,28 @@ int ra_ring_step_maps(int cp, int rank, int seq, int mode, int n_splits, int ste
   return ra_partition_position_stride(cp, mode);
 }
 
+int ra_ring_gather_part_maps(int cp, int rank, int seq, int mode, int n_splits, int parts,
+                             int part, ra_segmap* kmap, int* seg_shard, int* seg_row) {
+  if (!kmap || !seg_shard || !seg_row || cp <= 1 || rank < 0 || rank >= cp || parts < 1 ||
+      part < 0 || part >= parts)
+    return -1;
+  const int nsg = ra_partition_num_sub_groups(mode, n_splits);
+  if (nsg < 1 || nsg > RA_MAX_SEG) return -1;
+  const int entries = (cp - 1) * nsg;
+  std::memset(kmap, 0, sizeof(*kmap));
+  kmap->seg_len = ra_partition_local_chunk_len(cp, seq, mode, n_splits);
+  for (int e = part; e < entries; e += parts) {
+    if (kmap->n_seg >= RA_MAX_SEG) return -1;
+    const int s = 1 + e / nsg, i = e % nsg;
+    const int owner = (rank - s + cp) % cp;  // the shard s hops away
+    kmap->base[kmap->n_seg] = ra_partition_k_offset_for_source(cp, rank, seq, mode, n_splits, owner, i);
+    seg_shard[kmap->n_seg] = owner;
+    seg_row[kmap->n_seg] = i * kmap->seg_len;
+    ++kmap->n_seg;
+  }
+  return ra_partition_position_stride(cp, mode);
+}
+
 double ra_ring_step_visible_pairs(const ra_segmap* qmap, const ra_segmap* kmap, int stride,
                                   int causal, long long doc_len) {
   if (!qmap || !kmap) return 0.0;

@@ -392,26 +392,13 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
       // entries e = z, z + parts, ... so every part sees keys from all over the sequence
       bool aux_used[kAuxStreams] = {false, false, false};
       for (int z = 0; z < plan.parts; ++z) {
-        PosMap km;
-        std::memset(&km, 0, sizeof(km));
-        km.seg_len = kmap.seg_len;
+        ra_segmap ks;
         int seg_shard[RA_MAX_SEG], seg_row[RA_MAX_SEG];
-        int last_s = -1;
-        ra_segmap kq, ks;
-        for (int e = z; e < plan.entries; e += plan.parts) {
-          const int s = 1 + e / plan.nsg, i = e % plan.nsg;
-          if (s != last_s) {
-            stride = ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s, &kq, &ks);
-            RAB_REQUIRE(stride >= 1 && ks.n_seg == plan.nsg && ks.seg_len == kmap.seg_len,
-                        RA_ERR_INVALID, "ring prefill: bad partition");
-            last_s = s;
-          }
-          RAB_REQUIRE(km.n_seg < RA_MAX_SEG, RA_ERR_INVALID, "ring prefill: too many segments");
-          km.base[km.n_seg] = ks.base[i];
-          seg_shard[km.n_seg] = (r->rank - s + P) % P;
-          seg_row[km.n_seg] = i * kmap.seg_len;
-          ++km.n_seg;
-        }
+        stride = ra_ring_gather_part_maps(P, r->rank, c->seq, c->layout, c->n_splits, plan.parts, z,
+                                          &ks, seg_shard, seg_row);
+        RAB_REQUIRE(stride >= 1 && ks.n_seg >= 1 && ks.seg_len == kmap.seg_len, RA_ERR_INVALID,
+                    "ring prefill: bad partition");
+        const PosMap km = make_posmap(ks);
         ra_shape sh = shape;
         sh.seq_k = km.n_seg * km.seg_len;
         cudaStream_t st = stream;
