@@ -78,6 +78,14 @@ RA_API int ra_version(void);
  * Synchronises the device. No counterpart in the reference (its kernels have no waits). */
 RA_API int ra_device_status(int out[4]);
 
+/* Test hooks for the bounded waits; no counterpart in the reference. The limit of every
+ * device-side wait of the tcgen05 step kernel (default 2 s; 0 restores the default), and a
+ * switch that makes that kernel's TMA producer stop after `items` K/V tiles (negative = off),
+ * so that a test can watch a wait run out: the kernel returns, ra_device_status reports
+ * RA_ERR_DEVICE_WAIT, nothing is accessed out of bounds. Process-wide; not for production use. */
+RA_API void ra_debug_set_wait_limit_ns(unsigned long long ns);
+RA_API void ra_debug_stall_producer_after(int items);
+
 /* ------------------------------------------------------------------ prefill ---- */
 
 /* out = 0, l = 0, m = -inf. Replaces launch_attention_init (src/attention.hpp:73,
@@ -112,6 +120,8 @@ RA_API int ra_attention_step_segmented(const float* q, const float* k, const flo
 #define RA_STEP_FRESH 2u     /* the state is known to be empty: overwrite, do not read it */
 #define RA_STEP_FINALIZE 4u  /* after folding this step, divide out by l (as ra_attention_finalize) */
 #define RA_STEP_FORCE_SIMT 8u /* run the SIMT kernel whatever the head_dim (cross-checks) */
+#define RA_STEP_P_IN_SMEM 16u /* tcgen05 kernel: stage P through shared memory instead of tensor
+                               * memory (the second, cross-checking form of the same kernel) */
 
 /* The general step every other step entry point funnels into: any dtype, segmented
  * positions with a stride, optional document mask (visible only if
@@ -334,11 +344,31 @@ typedef struct ra_ring_result {
  * normalised, lse (B,H,Sloc) or NULL. K/V rotate rank -> rank+1 on a side stream,
  * double-buffered, while the step kernel runs (src/ring_loop_fp16.cu:638-708).
  * `kv_work` must hold ra_ring_prefill_workspace_bytes bytes. Returns after enqueueing
- * unless `result` is non-NULL, in which case it synchronises and fills the timings. */
+ * unless `result` is non-NULL, in which case it synchronises, fills the timings and returns
+ * RA_ERR_DEVICE_WAIT if a bounded device-side wait ran out. Callers that do not synchronise
+ * here poll ra_device_status themselves. */
 RA_API size_t ra_ring_prefill_workspace_bytes(const ra_ring* r, const ra_ring_config* cfg);
 RA_API int ra_ring_prefill(ra_ring* r, const ra_ring_config* cfg, const void* q, const void* k,
                            const void* v, float* out, float* lse, void* kv_work,
                            size_t kv_work_bytes, ra_stream stream, ra_ring_result* result);
+
+/* What ra_ring_prefill will do for cfg on this rank: the schedule taken (RA_SCHEDULE_RING or
+ * _GATHER), the number of key parts the gather schedule folds side by side (1 otherwise), and
+ * how many kernels of this library one pass launches (step kernels plus the merge of partial
+ * states). Host only. The reference prints its mode per run (apps/ring_attention_cli/main.cu:371-377). */
+RA_API int ra_ring_prefill_plan(const ra_ring* r, const ra_ring_config* cfg, int* schedule,
+                                int* key_parts, int* launches);
+
+/* The same pass from HOST buffers holding this rank's shards (pinned memory recommended): K and
+ * V are uploaded first so that the pass's transfers start while Q is still on its way, the
+ * output (and lse, if not NULL) comes back to the host, and the call returns after everything
+ * has completed. Device staging lives in the ring handle and grows on demand. The reference
+ * uploads inside its timed pass too (src/ring_loop_fp16.cu:624-626). `result`, if not NULL,
+ * gets total_ms = upload + pass + download, comp_ms = the pass alone, wait_ms = the rest.
+ * Returns RA_ERR_DEVICE_WAIT when a bounded device-side wait ran out during the pass. */
+RA_API int ra_ring_prefill_host(ra_ring* r, const ra_ring_config* cfg, const void* q_host,
+                                const void* k_host, const void* v_host, float* out_host,
+                                float* lse_host, ra_ring_result* result);
 
 /* One multi-rank decode step. Replaces run_ring_decode_step (src/ring_decode.hpp:67-69,
  * src/ring_decode.cu:85-226): owner appends, every rank folds its local shard, partials

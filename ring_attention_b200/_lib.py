@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libring_attention_b200.so")
 
 RA_F32, RA_F16, RA_BF16 = 0, 1, 2
 RA_STEP_CAUSAL, RA_STEP_FRESH, RA_STEP_FINALIZE, RA_STEP_FORCE_SIMT = 1, 2, 4, 8
+RA_STEP_P_IN_SMEM = 16
 RA_MAX_SEG = 16
 
 STATUS_NAMES = {0: "RA_OK", 1: "RA_ERR_INVALID", 2: "RA_ERR_CUDA", 3: "RA_ERR_UNSUPPORTED",
@@ -133,11 +134,16 @@ _SIG = {
     "ra_ring_prefill_workspace_bytes": (C.c_size_t, [_P, C.POINTER(RingConfig)]),
     "ra_ring_prefill": (C.c_int, [_P, C.POINTER(RingConfig), _P, _P, _P, _P, _P, _P, C.c_size_t,
                                   _P, C.POINTER(RingResult)]),
+    "ra_ring_prefill_plan": (C.c_int, [_P, C.POINTER(RingConfig), C.POINTER(C.c_int),
+                                       C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ra_ring_prefill_host": (C.c_int, [_P, C.POINTER(RingConfig), _P, _P, _P, _P, _P,
+                                       C.POINTER(RingResult)]),
     "ra_ring_decode_step": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_int, _P,
                                       C.POINTER(C.c_int), _P, _P, C.POINTER(RingResult)]),
     "ra_ring_decode_step_raw": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P,
                                           C.c_int, C.c_int, _P, _P, C.POINTER(RingResult)]),
-    "ra_debug_set_p_in_tmem": (None, [C.c_int]),
+    "ra_debug_set_wait_limit_ns": (None, [C.c_ulonglong]),
+    "ra_debug_stall_producer_after": (None, [C.c_int]),
 }
 
 _lib = None

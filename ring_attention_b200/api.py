@@ -88,10 +88,13 @@ def launch_attention_step_segmented(q, k, v, out, m, l, shape, qmap: SegMap, kma
 
 
 def attention_step_ex(q, k, v, out, m, l, shape, qmap, kmap, pos_stride=1, causal=False,
-                      fresh=False, finalize=False, force_simt=False, doc_len=0, kv_row_stride=0):
-    """General step: any dtype, segment maps with a stride, document mask, fused init/finalize."""
+                      fresh=False, finalize=False, force_simt=False, doc_len=0, kv_row_stride=0,
+                      p_in_smem=False):
+    """General step: any dtype, segment maps with a stride, document mask, fused init/finalize.
+    ``p_in_smem`` selects the tcgen05 kernel's second form (P staged through shared memory)."""
     flags = ((RA_STEP_CAUSAL if causal else 0) | (RA_STEP_FRESH if fresh else 0) |
-             (RA_STEP_FINALIZE if finalize else 0) | (RA_STEP_FORCE_SIMT if force_simt else 0))
+             (RA_STEP_FINALIZE if finalize else 0) | (RA_STEP_FORCE_SIMT if force_simt else 0) |
+             (_lib.RA_STEP_P_IN_SMEM if p_in_smem else 0))
     check(lib().ra_attention_step_ex(_dtype(q), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(m),
                                      _ptr(l), C.byref(shape.c()), C.byref(qmap), C.byref(kmap),
                                      pos_stride, flags, doc_len, kv_row_stride, _stream()))
@@ -396,6 +399,34 @@ class Ring:
         if timed:
             ret.append(res)
         return ret[0] if len(ret) == 1 else tuple(ret)
+
+    def _cfg(self, B, H, kvH, seq, D, dtype, causal, layout, n_splits, doc_len, schedule):
+        return RingConfig(B, H, kvH, seq, D, dtype, int(causal), layout, n_splits, doc_len,
+                          {"auto": 0, "ring": 1, "gather": 2}[schedule])
+
+    def plan(self, *, batch, heads, kv_heads, seq, head_dim, dtype=torch.float16, causal=True, layout=0,
+             n_splits=2, doc_len=0, schedule="auto"):
+        """(schedule name, key parts, kernel launches per pass) of ``prefill`` for this config."""
+        cfg = self._cfg(batch, heads, kv_heads, seq, head_dim, _DT[dtype], causal, layout, n_splits,
+                        doc_len, schedule)
+        sched, parts, launches = C.c_int(), C.c_int(), C.c_int()
+        check(lib().ra_ring_prefill_plan(self._h, C.byref(cfg), C.byref(sched), C.byref(parts),
+                                         C.byref(launches)))
+        return {1: "ring", 2: "gather"}[sched.value], parts.value, launches.value
+
+    def prefill_host(self, q, k, v, out, *, seq, causal, layout=0, n_splits=2, doc_len=0, lse=None,
+                     schedule="auto", timed=False):
+        """The pass from host tensors (pinned) holding this rank's shards into the host tensor
+        ``out``; returns after completion (``ra_ring_prefill_host``; the reference uploads inside
+        its timed pass too, src/ring_loop_fp16.cu:624-626)."""
+        B, H, sloc, D = q.shape
+        cfg = self._cfg(B, H, k.shape[1], seq, D, _dtype(q), causal, layout, n_splits, doc_len, schedule)
+        res = RingResult()
+        check(lib().ra_ring_prefill_host(self._h, C.byref(cfg), q.data_ptr(), k.data_ptr(),
+                                         v.data_ptr(), out.data_ptr(),
+                                         lse.data_ptr() if lse is not None else None,
+                                         C.byref(res) if timed else None))
+        return res if timed else None
 
     def decode_step(self, q, k_new, v_new, owner_rank, cache: DeviceKVCache, current_len_per_rank,
                     out, timed=False):

@@ -9,7 +9,8 @@
 
 namespace rab {
 
-void set_tc_p_in_tmem(int on);
+void set_tc_wait_limit_ns(unsigned long long ns);
+void set_tc_stall_after(int items);
 
 namespace {
 
@@ -212,8 +213,8 @@ int ra_attention_step_stacked(int dtype, const void* q, const void* k, const voi
                       static_cast<cudaStream_t>(stream));
 }
 
-// Test hook: 1 = keep P in tensor memory (default), 0 = stage P through shared memory.
-RA_API void ra_debug_set_p_in_tmem(int on) { rab::set_tc_p_in_tmem(on); }
+RA_API void ra_debug_set_wait_limit_ns(unsigned long long ns) { rab::set_tc_wait_limit_ns(ns); }
+RA_API void ra_debug_stall_producer_after(int items) { rab::set_tc_stall_after(items); }
 
 
 /* ------------------------------------------------ whole attention, device buffers ---- */
@@ -283,25 +284,32 @@ int ra_prefill_host(int dtype, const void* q_host, const void* k_host, const voi
   struct Scratch {
     void* p = nullptr;
     size_t bytes = 0;
-    int dev = -1;
+    int sm_count = 0;
     cudaStream_t stream = nullptr, s_in = nullptr, s_out = nullptr;
     cudaEvent_t e_in[kHostPipeEvents], e_done[kHostPipeEvents];
   };
-  thread_local Scratch sc;
+  // one per device and host thread: streams, events and the buffer always belong to `dev`
+  thread_local Scratch scratch_of_device[64];
   int dev = 0;
   RAB_CUDA(cudaGetDevice(&dev));
+  RAB_REQUIRE(dev >= 0 && dev < 64, RA_ERR_INVALID, "device index %d out of range", dev);
+  Scratch& sc = scratch_of_device[dev];
   const size_t a256 = 255;
   const size_t need = ((qn * es + a256) & ~a256) + 2 * ((kn * es + a256) & ~a256) +
                       ((qn * 4 + a256) & ~a256) + 3 * ((rows * 4 + a256) & ~a256);
-  if (sc.dev != dev || sc.bytes < need) {
-    if (sc.p && sc.dev == dev) RAB_CUDA(cudaFree(sc.p));
+  if (sc.stream == nullptr) {
+    RAB_CUDA(cudaStreamCreateWithFlags(&sc.stream, cudaStreamNonBlocking));
+    RAB_CUDA(cudaDeviceGetAttribute(&sc.sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if (sc.bytes < need) {
+    if (sc.p) {
+      RAB_CUDA(cudaStreamSynchronize(sc.stream));
+      RAB_CUDA(cudaFree(sc.p));
+    }
     sc.p = nullptr;
     sc.bytes = 0;
     RAB_CUDA(cudaMalloc(&sc.p, need));
     sc.bytes = need;
-    if (sc.dev != dev || sc.stream == nullptr)
-      RAB_CUDA(cudaStreamCreateWithFlags(&sc.stream, cudaStreamNonBlocking));
-    sc.dev = dev;
   }
   unsigned char* base = static_cast<unsigned char*>(sc.p);
   void* dq = base;
@@ -332,7 +340,7 @@ int ra_prefill_host(int dtype, const void* q_host, const void* k_host, const voi
   int groups = 1, bh_per_group = bh_total;
   if (kvH == s->heads && bh_total >= 2 && s->seq_q > 0) {
     const int qblocks = (s->seq_q + 255) / 256;
-    bh_per_group = std::max(1, (2 * 148 + qblocks - 1) / qblocks);
+    bh_per_group = std::max(1, (2 * sc.sm_count + qblocks - 1) / qblocks);
     groups = (bh_total + bh_per_group - 1) / bh_per_group;
     if (groups > kHostPipeEvents) {
       bh_per_group = (bh_total + kHostPipeEvents - 1) / kHostPipeEvents;
@@ -351,8 +359,10 @@ int ra_prefill_host(int dtype, const void* q_host, const void* k_host, const voi
       if (rc != RA_OK) return rc;
       RAB_CUDA(cudaMemcpyAsync(lse_host, dlse, rows * 4, cudaMemcpyDeviceToHost, st));
     }
+    rc = enqueue_status_read(st);
+    if (rc != RA_OK) return rc;
     RAB_CUDA(cudaStreamSynchronize(st));
-    return RA_OK;
+    return status_after_sync();
   }
   if (sc.s_in == nullptr) {
     RAB_CUDA(cudaStreamCreateWithFlags(&sc.s_in, cudaStreamNonBlocking));
@@ -382,10 +392,14 @@ int ra_prefill_host(int dtype, const void* q_host, const void* k_host, const voi
     ra_shape gs{1, nbh, s->seq_q, s->seq_k, s->head_dim, nbh};
     int rc = step_ex(dtype, gq, gk, gv, dout + qo, dm + ro, dl + ro, gs, qm, km, stride, f,
                      doc_len, 0, st);
-    if (rc != RA_OK) return rc;
-    if (lse_host) {
+    if (rc == RA_OK && lse_host)
       rc = ra_attention_lse(dm + ro, dl + ro, dlse + ro, static_cast<size_t>(nbh) * s->seq_q, st);
-      if (rc != RA_OK) return rc;
+    if (rc != RA_OK) {
+      // leave no copy in flight on the caller's buffers
+      cudaStreamSynchronize(sc.s_in);
+      cudaStreamSynchronize(st);
+      cudaStreamSynchronize(sc.s_out);
+      return rc;
     }
     RAB_CUDA(cudaEventRecord(sc.e_done[g], st));
     RAB_CUDA(cudaStreamWaitEvent(sc.s_out, sc.e_done[g], 0));
@@ -395,9 +409,11 @@ int ra_prefill_host(int dtype, const void* q_host, const void* k_host, const voi
       RAB_CUDA(cudaMemcpyAsync(lse_host + ro, dlse + ro, static_cast<size_t>(nbh) * s->seq_q * 4,
                                cudaMemcpyDeviceToHost, sc.s_out));
   }
+  const int rc_status = enqueue_status_read(st);
+  if (rc_status != RA_OK) return rc_status;
   RAB_CUDA(cudaStreamSynchronize(sc.s_out));
   RAB_CUDA(cudaStreamSynchronize(st));
-  return RA_OK;
+  return status_after_sync();
 }
 
 /* ------------------------------------------------------------------------ KV cache ---- */
@@ -485,12 +501,12 @@ int ra_local_decode_step(const void* q, const ra_kv_cache* cache, int heads, int
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   ra_shape s{cache->batch, heads, 1, cache->current_len, cache->head_dim, cache->kv_heads};
   const size_t rows = static_cast<size_t>(cache->batch) * heads;
-  // m and l live behind the partials in the per-device decode workspace request: ask for a
-  // workspace with room for both.
+  // m and l of this one-shot state live in a per-device scratch that is allocated once and
+  // grows on demand (not safe for concurrent streams, like the decode workspace itself)
   float* ml = nullptr;
-  RAB_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&ml), 2 * rows * sizeof(float), stream));
+  int rc = decode_ml_scratch(2 * rows, &ml);
+  if (rc != RA_OK) return rc;
   // init and the division by l ride on the fold of the split partials: two launches in all
-  int rc = RA_OK;
   if (cache->current_len > 0) {
     rc = decode_step(cache->dtype, q, cache->k, cache->v, out, ml, ml + rows, s, q_pos_global,
                      cache_k_offset, causal, stream, cache->s_max, nullptr, 0,
@@ -498,7 +514,6 @@ int ra_local_decode_step(const void* q, const ra_kv_cache* cache, int heads, int
   } else {
     rc = launch_init(out, ml, ml + rows, rows * cache->head_dim, rows, stream);
   }
-  cudaFreeAsync(ml, stream);
   return rc;
 }
 

@@ -51,6 +51,13 @@ inline int kv_heads_of(const ra_shape& s) { return s.kv_heads > 0 ? s.kv_heads :
 // library returns at once, so a protocol bug costs seconds, never a hung GPU.
 int* device_status_ptr();  // device address of the 4-int status word of the current device
 int read_device_status(int out[4], bool clear);
+// For entry points that end with a synchronisation of `stream`: enqueue_status_read in front
+// of it, status_after_sync behind it (RA_ERR_DEVICE_WAIT when a wait ran out; the word stays
+// set, so every later launch returns at once, until ra_device_status reads and clears it).
+int enqueue_status_read(cudaStream_t stream);
+int status_after_sync();
+// Scratch for the (m, l) of the local decode op, per device, grown on demand.
+int decode_ml_scratch(size_t floats, float** out);
 
 // ---- position maps ------------------------------------------------------------------
 // Kernel-side copy of a segment map: local row i -> base[i / seg_len] + (i % seg_len) * stride.

@@ -2,25 +2,24 @@
 // hot path. Replaces the reference's split + reduce kernels (src/attention_decode.cu:73-277).
 //
 // What bounds it: every K and V row of the local shard is read exactly once from HBM, so
-// the kernel is built around bytes in flight, not arithmetic.
+// the kernels are built around bytes in flight, not arithmetic.
 //  - One block per (split, KV head, batch row) serves ALL query heads that map to that KV
 //    head (h % kv_heads), so grouped-query attention reads each cached row once instead of
 //    once per query head (the reference re-reads it per head, src/attention_decode.cu:88).
-//  - K/V rows stream through a 4-stage shared-memory ring filled with 16-byte cp.async
-//    copies (fully coalesced: consecutive threads copy consecutive 16-byte pieces of
-//    consecutive rows), which keeps tens of KB per SM in flight without holding them in
-//    registers.
-//  - A group of `LPR` lanes owns a row: each lane keeps its slice of q (pre-scaled) for every
-//    head of the group, the dot product finishes with log2(LPR) shuffles, and each lane
-//    group carries its own running (m, l, out) so no cross-lane traffic is needed until
-//    the end, where a warp-shuffle log-sum-exp merge and one shared-memory pass combine the
-//    lane groups and warps of the block.
 //  - The split count is chosen so the grid is about three waves of the SM count.
-//  - fp16 / bf16 caches with head_dim >= 64 take the tensor-core kernel further down
-//    (decode_mma_kernel): the same streaming structure with the two contractions of each
-//    16-key block on mma.sync, because the SIMT form is bound by instruction issue (about 80
-//    warp instructions per cached row) at 43 % of HBM speed, the MMA form by the copy (87 %).
-//    fp32 caches and head_dim 32 keep the SIMT kernel.
+//  - decode_mma_kernel (fp16 / bf16 caches, head_dim >= 64) is the fast path: K/V rows stream
+//    through a 5-8-stage shared-memory ring of 64-key stages filled with 16-byte cp.async
+//    copies (fully coalesced, XOR-swizzled), and per 16-key block a warp does both
+//    contractions on mma.sync m16n8k16 with the up to 16 grouped query heads as M rows
+//    (ldmatrix / ldmatrix.trans), online softmax with warp-shuffle row maxima and a lazy
+//    rescale; warps are merged through shared memory. The tensor cores are there to get under
+//    the instruction-issue bound (about 5 instead of about 80 warp instructions per cached
+//    row), the kernel is bound by the copy (0.87 of the measured HBM copy bandwidth).
+//  - decode_split_kernel (fp32 caches, head_dim 32) is the SIMT form of the same structure
+//    with a 4-stage ring: a group of `LPR` lanes owns a row, each lane keeps its slice of q
+//    (pre-scaled) for every head of the group, the dot product finishes with log2(LPR)
+//    shuffles, each lane group carries its own running (m, l, out), and a warp-shuffle
+//    log-sum-exp merge plus one shared-memory pass combine lane groups and warps.
 // Partials (m, l, out) per (split, batch, head) go to a workspace; a second tiny kernel
 // folds them into the persistent state (src/attention_decode.cu:228-277 does the same for
 // its fixed 8 splits).
@@ -696,6 +695,29 @@ int ensure_workspace(size_t need, void** out) {
   *out = w.ptr;
   return RA_OK;
 }
+
+}  // namespace
+
+int decode_ml_scratch(size_t floats, float** out) {
+  static DevWorkspace ml[64];
+  int dev = 0;
+  RAB_CUDA(cudaGetDevice(&dev));
+  RAB_REQUIRE(dev >= 0 && dev < 64, RA_ERR_INVALID, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_ws_mu);
+  DevWorkspace& w = ml[dev];
+  const size_t need = floats * sizeof(float);
+  if (w.bytes < need) {
+    if (w.ptr) RAB_CUDA(cudaFree(w.ptr));
+    w.ptr = nullptr;
+    w.bytes = 0;
+    RAB_CUDA(cudaMalloc(&w.ptr, need));
+    w.bytes = need;
+  }
+  *out = static_cast<float*>(w.ptr);
+  return RA_OK;
+}
+
+namespace {
 
 template <typename T, int D>
 int launch_decode_typed(const void* q, const void* k, const void* v, float* out, float* m,

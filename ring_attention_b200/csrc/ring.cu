@@ -19,6 +19,7 @@
 //
 // NCCL is loaded with dlopen at ring creation, so the rest of the library works without it.
 #include <dlfcn.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <mutex>
 #include <vector>
@@ -86,7 +87,37 @@ bool load_nccl() {
     }                                                                                       \
   } while (0)
 
-constexpr int kMaxRanks = 64;
+constexpr int kMaxRanks = 16;  // one NVSwitch box
+
+// NVTX range around one ring / decode step (visible in Nsight timelines; a no-op without a tool).
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
+
+// NCCL calls between GroupStart and GroupEnd: remember the first failure but always close the
+// group, so that a failed call cannot leave the thread's NCCL group open (every later NCCL call
+// of the thread, the caller's own included, would silently queue into it).
+struct NcclGroup {
+  int first = 0;
+  const char* what = "";
+  NcclGroup() { note(g_nccl.GroupStart(), "ncclGroupStart"); }
+  void note(int r, const char* w) {
+    if (r != 0 && first == 0) {
+      first = r;
+      what = w;
+    }
+  }
+  int end() {
+    note(g_nccl.GroupEnd(), "ncclGroupEnd");
+    if (first != 0) {
+      ::rab::set_error("NCCL error %d (%s) in %s", first,
+                       g_nccl.GetErrorString ? g_nccl.GetErrorString(first) : "?", what);
+      return RA_ERR_NCCL;
+    }
+    return RA_OK;
+  }
+};
 constexpr int kAuxStreams = 3;
 constexpr int kMaxKeyParts = 7;  // + the own-shard state = the 8 states one merge takes
 
@@ -109,6 +140,11 @@ struct ra_ring {
   // decode buffers, grown on demand: send [O|m|l] block and cp * block receive area
   float* dec_buf;
   size_t dec_bytes;
+  // host-buffer pass (ra_ring_prefill_host): device staging, grown on demand
+  void* host_buf;
+  size_t host_bytes;
+  cudaStream_t host_stream, host_q_stream;
+  cudaEvent_t ev_host_q, ev_host_begin, ev_host_end;
 };
 
 static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
@@ -121,6 +157,13 @@ static int ring_finish_create(int rank, int cp, ncclComm_t comm, bool own, ra_ri
   r->own_comm = own;
   r->dec_buf = nullptr;
   r->dec_bytes = 0;
+  r->host_buf = nullptr;
+  r->host_bytes = 0;
+  RAB_CUDA(cudaStreamCreateWithFlags(&r->host_stream, cudaStreamNonBlocking));
+  RAB_CUDA(cudaStreamCreateWithFlags(&r->host_q_stream, cudaStreamNonBlocking));
+  RAB_CUDA(cudaEventCreateWithFlags(&r->ev_host_q, cudaEventDisableTiming));
+  RAB_CUDA(cudaEventCreate(&r->ev_host_begin));
+  RAB_CUDA(cudaEventCreate(&r->ev_host_end));
   // The transfer stream gets the highest priority: the step kernel keeps every SM full (one
   // block per SM, all registers), so the few blocks of a send/recv kernel can only run on SMs
   // the block scheduler hands them first. Without the priority they queue behind the step
@@ -203,6 +246,14 @@ void ra_ring_destroy(ra_ring* r) {
     cudaEventDestroy(r->ev_comp_begin[i]);
   }
   if (r->dec_buf) cudaFree(r->dec_buf);
+  cudaStreamSynchronize(r->host_stream);
+  cudaStreamSynchronize(r->host_q_stream);
+  if (r->host_buf) cudaFree(r->host_buf);
+  cudaStreamDestroy(r->host_stream);
+  cudaStreamDestroy(r->host_q_stream);
+  cudaEventDestroy(r->ev_host_q);
+  cudaEventDestroy(r->ev_host_begin);
+  cudaEventDestroy(r->ev_host_end);
   delete r;
 }
 
@@ -299,9 +350,38 @@ size_t ra_ring_prefill_workspace_bytes(const ra_ring* r, const ra_ring_config* c
   return kv + 2 * ml + 256;
 }
 
-int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const void* k,
-                    const void* v, float* out, float* lse, void* kv_work, size_t kv_work_bytes,
-                    ra_stream stream_, ra_ring_result* result) {
+int ra_ring_prefill_plan(const ra_ring* r, const ra_ring_config* c, int* schedule, int* key_parts,
+                         int* launches) {
+  const int rc = check_cfg(r, c);
+  if (rc != RA_OK) return rc;
+  const int kvH = c->kv_heads > 0 ? c->kv_heads : c->heads;
+  const size_t es = c->dtype == RA_F32 ? 4 : 2;
+  const size_t kv_raw =
+      static_cast<size_t>(c->batch) * kvH * (c->seq / r->cp) * c->head_dim * es;
+  int sched = RA_SCHEDULE_RING, parts = 1, n = r->cp;
+  if (use_gather(r, c, kv_raw)) {
+    sched = RA_SCHEDULE_GATHER;
+    const GatherPlan g = gather_plan(r, c);
+    if (g.stacked) {
+      parts = g.parts;
+      n = 1 + g.parts + (g.parts >= 2 ? 1 : 0);  // own shard, the parts, the merge
+    }
+  }
+  if (schedule) *schedule = sched;
+  if (key_parts) *key_parts = parts;
+  if (launches) *launches = n;
+  return RA_OK;
+}
+
+}  // extern "C"
+
+// The pass itself. `q_ready`, when set, is an event the compute stream waits for after the
+// transfers of the pass have been started and before the first step (the host-buffer entry
+// point uploads Q on another stream while K/V already travel).
+static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q, const void* k,
+                             const void* v, float* out, float* lse, void* kv_work,
+                             size_t kv_work_bytes, ra_stream stream_, ra_ring_result* result,
+                             cudaEvent_t q_ready) {
   int rc = check_cfg(r, c);
   if (rc != RA_OK) return rc;
   RAB_REQUIRE(q && k && v && out && kv_work, RA_ERR_INVALID, "ring prefill: null argument");
@@ -347,13 +427,16 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
   RAB_CUDA(cudaEventRecord(r->ev_start, stream));
   RAB_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_start, 0));
   if (gather) {
+    NvtxRange range("ring prefill: all-gather K/V");
     RAB_CUDA(cudaEventRecord(r->ev_comm_begin[0], r->comm_stream));
-    RAB_NCCL(g_nccl.GroupStart());
-    RAB_NCCL(g_nccl.AllGather(k, buf_k[0], kv_raw, kNcclInt8, r->comm, r->comm_stream));
-    RAB_NCCL(g_nccl.AllGather(v, buf_v[0], kv_raw, kNcclInt8, r->comm, r->comm_stream));
-    RAB_NCCL(g_nccl.GroupEnd());
+    NcclGroup grp;
+    grp.note(g_nccl.AllGather(k, buf_k[0], kv_raw, kNcclInt8, r->comm, r->comm_stream), "ncclAllGather(K)");
+    grp.note(g_nccl.AllGather(v, buf_v[0], kv_raw, kNcclInt8, r->comm, r->comm_stream), "ncclAllGather(V)");
+    rc = grp.end();
+    if (rc != RA_OK) return rc;
     RAB_CUDA(cudaEventRecord(r->ev_comm[0], r->comm_stream));
   }
+  if (q_ready) RAB_CUDA(cudaStreamWaitEvent(stream, q_ready, 0));
   int n_launch = 0;  // timed compute intervals of this pass
   if (gather) {
     const bool split = plan.parts >= 2;
@@ -433,20 +516,26 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
     n_launch = 2;
   }
   for (int s = 0; s < P && !gather; ++s) {
+    NvtxRange range("ring prefill: step");
     const void* cur_k = s == 0 ? k : buf_k[(s - 1) & 1];
     const void* cur_v = s == 0 ? v : buf_v[(s - 1) & 1];
     if (s < P - 1) {
       // the buffer about to be received into was the source of compute step s-1
       if (s >= 1) RAB_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_comp[s - 1], 0));
       RAB_CUDA(cudaEventRecord(r->ev_comm_begin[s], r->comm_stream));
-      RAB_NCCL(g_nccl.GroupStart());
-      RAB_NCCL(g_nccl.Send(cur_k, kv_raw, kNcclInt8, next, r->comm, r->comm_stream));
-      RAB_NCCL(g_nccl.Recv(buf_k[s & 1], kv_raw, kNcclInt8, prev, r->comm, r->comm_stream));
-      RAB_NCCL(g_nccl.Send(cur_v, kv_raw, kNcclInt8, next, r->comm, r->comm_stream));
-      RAB_NCCL(g_nccl.Recv(buf_v[s & 1], kv_raw, kNcclInt8, prev, r->comm, r->comm_stream));
-      RAB_NCCL(g_nccl.GroupEnd());
+      NcclGroup grp;
+      grp.note(g_nccl.Send(cur_k, kv_raw, kNcclInt8, next, r->comm, r->comm_stream), "ncclSend(K)");
+      grp.note(g_nccl.Recv(buf_k[s & 1], kv_raw, kNcclInt8, prev, r->comm, r->comm_stream), "ncclRecv(K)");
+      grp.note(g_nccl.Send(cur_v, kv_raw, kNcclInt8, next, r->comm, r->comm_stream), "ncclSend(V)");
+      grp.note(g_nccl.Recv(buf_v[s & 1], kv_raw, kNcclInt8, prev, r->comm, r->comm_stream), "ncclRecv(V)");
+      rc = grp.end();
+      if (rc != RA_OK) {
+        cudaStreamSynchronize(r->comm_stream);  // nothing of this pass may still write the workspace
+        return rc;
+      }
       RAB_CUDA(cudaEventRecord(r->ev_comm[s], r->comm_stream));
     }
+    if (s == 0 && q_ready) RAB_CUDA(cudaStreamWaitEvent(stream, q_ready, 0));
     if (s > 0) RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[s - 1], 0));
     ra_segmap qmap, kmap;
     const int stride =
@@ -458,7 +547,10 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
     RAB_CUDA(cudaEventRecord(r->ev_comp_begin[s], stream));
     rc = ra_attention_step_ex(c->dtype, q, cur_k, cur_v, out, m, l, &shape, &qmap, &kmap, stride,
                               flags, c->doc_len, 0, stream);
-    if (rc != RA_OK) return rc;
+    if (rc != RA_OK) {
+      cudaStreamSynchronize(r->comm_stream);  // transfers already queued write the workspace
+      return rc;
+    }
     RAB_CUDA(cudaEventRecord(r->ev_comp[s], stream));
     n_launch = s + 1;
   }
@@ -468,8 +560,12 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
   }
   RAB_CUDA(cudaEventRecord(r->ev_end, stream));
   if (result) {
+    rc = enqueue_status_read(stream);
+    if (rc != RA_OK) return rc;
     RAB_CUDA(cudaStreamSynchronize(stream));
     RAB_CUDA(cudaStreamSynchronize(r->comm_stream));
+    rc = status_after_sync();
+    if (rc != RA_OK) return rc;
     float ms = 0.f;
     double comp = 0.0, comm = 0.0;
     for (int s = 0; s < n_launch; ++s) {
@@ -490,6 +586,93 @@ int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const vo
   return RA_OK;
 }
 
+extern "C" {
+
+int ra_ring_prefill(ra_ring* r, const ra_ring_config* c, const void* q, const void* k,
+                    const void* v, float* out, float* lse, void* kv_work, size_t kv_work_bytes,
+                    ra_stream stream, ra_ring_result* result) {
+  return ring_prefill_impl(r, c, q, k, v, out, lse, kv_work, kv_work_bytes, stream, result, nullptr);
+}
+
+int ra_ring_prefill_host(ra_ring* r, const ra_ring_config* c, const void* q_host,
+                         const void* k_host, const void* v_host, float* out_host, float* lse_host,
+                         ra_ring_result* result) {
+  int rc = check_cfg(r, c);
+  if (rc != RA_OK) return rc;
+  RAB_REQUIRE(q_host && k_host && v_host && out_host, RA_ERR_INVALID,
+              "ring prefill (host): null argument");
+  NvtxRange range("ring prefill (host buffers)");
+  const int kvH = c->kv_heads > 0 ? c->kv_heads : c->heads;
+  const size_t es = c->dtype == RA_F32 ? 4 : 2;
+  const size_t sloc = static_cast<size_t>(c->seq / r->cp);
+  const size_t rows = static_cast<size_t>(c->batch) * c->heads * sloc;
+  const size_t q_bytes = rows * c->head_dim * es;
+  const size_t kv_raw = static_cast<size_t>(c->batch) * kvH * sloc * c->head_dim * es;
+  const size_t out_bytes = rows * c->head_dim * sizeof(float);
+  const size_t lse_bytes = rows * sizeof(float);
+  const size_t work_bytes = ra_ring_prefill_workspace_bytes(r, c);
+  const size_t need = align256(q_bytes) + 2 * align256(kv_raw) + align256(out_bytes) +
+                      align256(lse_bytes) + align256(work_bytes);
+  if (r->host_bytes < need) {
+    if (r->host_buf) {
+      RAB_CUDA(cudaStreamSynchronize(r->host_stream));
+      RAB_CUDA(cudaFree(r->host_buf));
+    }
+    r->host_buf = nullptr;
+    r->host_bytes = 0;
+    RAB_CUDA(cudaMalloc(&r->host_buf, need));
+    r->host_bytes = need;
+  }
+  unsigned char* p = static_cast<unsigned char*>(r->host_buf);
+  void* dq = p;
+  p += align256(q_bytes);
+  void* dk = p;
+  p += align256(kv_raw);
+  void* dv = p;
+  p += align256(kv_raw);
+  float* dout = reinterpret_cast<float*>(p);
+  p += align256(out_bytes);
+  float* dlse = reinterpret_cast<float*>(p);
+  p += align256(lse_bytes);
+  void* work = p;
+  cudaStream_t st = r->host_stream;
+  // K and V go first: the transfers of the pass (all-gather or first hop) need only them and
+  // start while Q is still on its way up on a second stream; the first step waits for Q.
+  RAB_CUDA(cudaEventRecord(r->ev_host_begin, st));
+  RAB_CUDA(cudaMemcpyAsync(dk, k_host, kv_raw, cudaMemcpyHostToDevice, st));
+  RAB_CUDA(cudaMemcpyAsync(dv, v_host, kv_raw, cudaMemcpyHostToDevice, st));
+  RAB_CUDA(cudaStreamWaitEvent(r->host_q_stream, r->ev_host_begin, 0));
+  RAB_CUDA(cudaMemcpyAsync(dq, q_host, q_bytes, cudaMemcpyHostToDevice, r->host_q_stream));
+  RAB_CUDA(cudaEventRecord(r->ev_host_q, r->host_q_stream));
+  ra_ring_result pass{};
+  rc = ring_prefill_impl(r, c, dq, dk, dv, dout, lse_host ? dlse : nullptr, work, work_bytes, st,
+                         nullptr, r->ev_host_q);
+  if (rc != RA_OK) {
+    cudaStreamSynchronize(r->host_q_stream);
+    cudaStreamSynchronize(st);
+    return rc;
+  }
+  RAB_CUDA(cudaMemcpyAsync(out_host, dout, out_bytes, cudaMemcpyDeviceToHost, st));
+  if (lse_host) RAB_CUDA(cudaMemcpyAsync(lse_host, dlse, lse_bytes, cudaMemcpyDeviceToHost, st));
+  RAB_CUDA(cudaEventRecord(r->ev_host_end, st));
+  rc = enqueue_status_read(st);
+  if (rc != RA_OK) return rc;
+  RAB_CUDA(cudaStreamSynchronize(st));
+  RAB_CUDA(cudaStreamSynchronize(r->comm_stream));
+  rc = status_after_sync();
+  if (rc != RA_OK) return rc;
+  if (result) {
+    float ms = 0.f, pass_ms = 0.f;
+    RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_host_begin, r->ev_host_end));
+    RAB_CUDA(cudaEventElapsedTime(&pass_ms, r->ev_start, r->ev_end));
+    result->total_ms = ms;           // upload + pass + download
+    result->comp_ms = pass_ms;       // the ring pass alone
+    result->comm_ms = 0.0;
+    result->wait_ms = ms - pass_ms;  // time spent on the host link outside the pass
+  }
+  return RA_OK;
+}
+
 int ra_ring_decode_step_raw(ra_ring* r, int dtype, int batch, int heads, int kv_heads,
                             int head_dim, const void* q, const void* k_cache, const void* v_cache,
                             int local_len, int s_max, float* out, ra_stream stream_,
@@ -498,6 +681,7 @@ int ra_ring_decode_step_raw(ra_ring* r, int dtype, int batch, int heads, int kv_
   RAB_REQUIRE(batch > 0 && heads > 0 && local_len >= 0 && local_len <= s_max, RA_ERR_INVALID,
               "ring decode: bad sizes (local_len=%d, s_max=%d)", local_len, s_max);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  NvtxRange range("ring decode step");
   const int D = head_dim;
   const size_t bh = static_cast<size_t>(batch) * heads;
   const size_t block = bh * D + 2 * bh;  // floats per rank: [O | m | l]
@@ -538,7 +722,11 @@ int ra_ring_decode_step_raw(ra_ring* r, int dtype, int batch, int heads, int kv_
   if (rc != RA_OK) return rc;
   RAB_CUDA(cudaEventRecord(r->ev_end, stream));
   if (result) {
+    rc = enqueue_status_read(stream);
+    if (rc != RA_OK) return rc;
     RAB_CUDA(cudaStreamSynchronize(stream));
+    rc = status_after_sync();
+    if (rc != RA_OK) return rc;
     float a = 0.f, b = 0.f, t = 0.f;
     RAB_CUDA(cudaEventElapsedTime(&a, r->ev_start, r->ev_comp[0]));
     RAB_CUDA(cudaEventElapsedTime(&b, r->ev_comp[0], r->ev_comm[0]));

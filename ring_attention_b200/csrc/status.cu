@@ -33,6 +33,41 @@ int* device_status_ptr() {
   return cache[dev];
 }
 
+// Pinned host mirror of the status word, one per device, for entry points that already end
+// with a stream synchronisation: they enqueue a 16-byte copy in front of that synchronisation
+// and look at the mirror afterwards, so the check costs no extra round trip.
+int* status_mirror() {
+  static int* mirror[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!mirror[dev]) {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, 4 * sizeof(int), cudaHostAllocDefault) != cudaSuccess) return nullptr;
+    std::memset(p, 0, 4 * sizeof(int));
+    mirror[dev] = static_cast<int*>(p);
+  }
+  return mirror[dev];
+}
+
+int enqueue_status_read(cudaStream_t stream) {
+  int* d = device_status_ptr();
+  int* h = status_mirror();
+  RAB_REQUIRE(d && h, RA_ERR_CUDA, "device status word unavailable");
+  RAB_CUDA(cudaMemcpyAsync(h, d, 4 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+  return RA_OK;
+}
+
+int status_after_sync() {
+  const int* h = status_mirror();
+  if (h && h[0] != 0) {
+    set_error("a bounded device-side wait ran out (code %d, wait %d, block %d, tile %d): the "
+              "results of this call are invalid; ra_device_status() reads and clears the word",
+              h[0], h[1], h[2], h[3]);
+    return RA_ERR_DEVICE_WAIT;
+  }
+  return RA_OK;
+}
+
 int read_device_status(int out[4], bool clear) {
   int* p = device_status_ptr();
   RAB_REQUIRE(p != nullptr, RA_ERR_CUDA, "device status word unavailable");

@@ -13,27 +13,43 @@
 // Roles inside a block (384 threads)
 //   warp 0        TMA producer: Q tiles once, then K_j, V_j, K_j+1, ... into a shared-memory
 //                 ring of 128B-swizzled tiles (cp.async.bulk.tensor, no multicast).
-//   warp 1        MMA issuer (one lane): S_w = Q_w K_j^T and O_w += P_w V_j with fp32
-//                 accumulators in tensor memory; also allocates / frees tensor memory.
+//   warps 1, 2    MMA issuers, one per query tile: S_w = Q_w K_j^T and O_w += P_w V_j with fp32
+//                 accumulators in tensor memory. The whole warp runs the loop (uniform control
+//                 flow and descriptors), one elected lane executes tcgen05.mma / commit.
+//                 Warp 1 also allocates / frees tensor memory.
 //   warps 4-7     softmax for query tile 0: one thread per row reads S from tensor memory,
-//   warps 8-11    (tile 1) keeps the running max / sum, writes P as 16-bit back into tensor
-//                 memory (over S) or into shared memory, rescales O only when the row
-//                 maximum moved by more than 2^8, and runs the epilogue.
-//   The two query tiles ping-pong: while one tile's rows are in softmax the tensor core
-//   works on the other tile.
+//   warps 8-11    (tile 1) writes P = 2^(s * scale - m_ref) as 16-bit back into tensor memory
+//                 (or into shared memory), keeps the row sum, and runs the epilogue. m_ref is
+//                 the row's reference point, set from the row maximum of the first tile the row
+//                 sees and moved (with a rescale of O and l) only when a tile's row sum shows
+//                 that some score ran more than 2^15 above it; the common tile needs neither
+//                 a row maximum nor a rescale.
+//   The two query tiles are independent streams (own issuing warp, own barriers): the tensor
+//   core works on one tile's MMAs while the other tile's rows are in their exponentials.
 //
-// Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+// Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D), and
+// at head_dim 64 a separate P0 / P1 of 64 columns each behind them (otherwise P overwrites S).
 //
-// Epilogue: the step's partial (O, m, l) is merged with the persistent state in HBM using
+// What bounds it: a timing probe of back-to-back tcgen05.mma from an elected lane gives 66 clk
+// per M128 N128 K16 instruction (shared-memory operands) and 33 clk at N = 64 with A in tensor
+// memory, i.e. the arithmetic rate; cta_group::2 pairs cost the same per SM. A pair of 128x128
+// tiles therefore needs ~1070 clk of tensor time at head_dim 64 (~2110 at 128) but 2048 clk of
+// the exp unit (16 ex2 per clock per SM) plus the rest of the softmax instructions: the
+// softmax warps, not the MMA issue, set the tile period at head_dim 64.
+//
+// Epilogue: the step's partial (O, m_ref, l) is merged with the persistent state in HBM using
 // the log-sum-exp merge, which is the same recurrence as folding the tiles one by one
 // (src/attention_step_fp16.cu:155-172), so the (out, m, l) contract of the reference holds:
-// unnormalised out, natural-log m, rows without a visible key untouched.
+// unnormalised out and l relative to a natural-log m (m is a reference point at or below the
+// running maximum, within 2^15; m + log(l) is the exact log-sum-exp), rows without a visible
+// key untouched.
 //
 // Every wait on an mbarrier is bounded: when one runs out the block records where in the
 // device status word, all roles leave their loops, tensor memory is freed and the kernel
 // returns; later blocks see the status word and return at once.
 #include <cuda.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -48,22 +64,8 @@ constexpr int kBN = 128;           // keys per tile
 constexpr int kQBlock = 2 * kBM;   // query rows per block
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O when the max moved > 2^8
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
-
-#ifdef RAB_TRACE
-// Bring-up timeline (compiled only with -DRAB_TRACE): clock64 stamps of block (0,0) for the
-// first 64 tiles; roles 0/1 = first lane of the two softmax groups, 2 = the MMA lane.
-__device__ long long g_trace[3][64][8];
-#define RAB_TR(role, tile, k)                                                  \
-  do {                                                                         \
-    if (trace_on && (tile) < 64) g_trace[role][tile][k] = clock64();          \
-  } while (0)
-#else
-#define RAB_TR(role, tile, k) \
-  do {                        \
-  } while (0)
-#endif
+constexpr float kRowSumLimit = 32768.f;  // a tile's row sum of P above this moves the reference
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // default limit of every wait: 2 s
 
 // ---- PTX wrappers -------------------------------------------------------------------
 __device__ inline unsigned smem_u32(const void* p) {
@@ -90,6 +92,28 @@ __device__ inline bool mbar_try_wait(unsigned bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking form: has the phase with this parity completed?
+__device__ inline bool mbar_test_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// One lane of a converged warp (the same lane every time for a full mask).
+__device__ inline bool elect_one() {
+  unsigned pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ inline unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -99,7 +123,7 @@ __device__ inline unsigned long long global_ns() {
 // Bounded wait. Returns false when the block is aborting (own limit reached or another
 // role flagged it). `which` identifies the wait in the status word.
 __device__ inline bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag,
-                                 int* status, int which, int tile) {
+                                 int* status, int which, int tile, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   unsigned spins = 0;
@@ -107,7 +131,7 @@ __device__ inline bool mbar_wait(unsigned bar, unsigned parity, volatile int* ab
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 255u) == 0) {
       if (*abort_flag) return false;
-      if (global_ns() - t0 > kWaitLimitNs) {
+      if (global_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (atomicCAS(&status[0], 0, RA_ERR_DEVICE_WAIT) == 0) {
           status[1] = which;
@@ -273,37 +297,12 @@ __device__ inline float2 fadd2(float2 a, float2 b) {
         "l"(*reinterpret_cast<unsigned long long*>(&b)));
   return d;
 }
-// 2^x for two lanes on the FMA pipe: n = round(x) through the 1.5 * 2^23 rounding constant,
-// 2^(x - n) by a degree-3 polynomial on [-0.5, 0.5] (max relative error 7.5e-5, below the
-// 2.4e-4 rounding of 16-bit P), n added to the exponent bits. x is clamped at -125 so that the
-// exponent cannot wrap; 2^-125 becomes 0 when P is rounded to 16 bits.
 // Register split between the producer / MMA warpgroup and the two softmax warpgroups
 // (128 * LO + 256 * HI <= 65536).
 #ifndef RAB_REGS_LO
 #define RAB_REGS_LO 72
 #define RAB_REGS_HI 216
 #endif
-#ifndef RAB_POLY_NUM
-#define RAB_POLY_NUM 0
-#define RAB_POLY_DEN 1
-#endif
-constexpr int kPolyNum = RAB_POLY_NUM, kPolyDen = RAB_POLY_DEN;  // share of every second pair
-__device__ inline float2 exp2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -125.f);
-  x.y = fmaxf(x.y, -125.f);
-  const float2 magic = make_float2(12582912.f, 12582912.f);
-  const float2 t = fadd2(x, magic);
-  const float2 n = fadd2(t, make_float2(-12582912.f, -12582912.f));
-  const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
-  float2 p = ffma2(f, make_float2(0.0551716685f, 0.0551716685f),
-                   make_float2(0.2426111251f, 0.2426111251f));
-  p = ffma2(p, f, make_float2(0.6932609677f, 0.6932609677f));
-  p = ffma2(p, f, make_float2(0.9999280572f, 0.9999280572f));
-  float2 r;
-  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
-  return r;
-}
 template <bool kBf16>
 __device__ inline unsigned pack16(float lo, float hi) {
 
@@ -411,6 +410,8 @@ struct TcArgs {
   unsigned flags;
   long long doc_len;
   int* status;
+  unsigned long long wait_ns;  // limit of every device-side wait
+  int stall_after;             // test hook: the producer stops after this many ring items (< 0: off)
 };
 
 // DR is the head_dim of the tensors in memory: D, or 32 on the 64-wide kernel (see launch_cfg).
@@ -441,11 +442,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // provably warp-uniform
   const int lane = tid & 31;
-#ifdef RAB_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
-#endif
 
   // An earlier block gave up: leave at once (the vote makes the decision block-uniform).
   if (__syncthreads_or(*reinterpret_cast<volatile int*>(a.status) != 0)) return;
@@ -480,7 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(bar_q_full + 8, 1);
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_kv_full + 8 * s, 1);
-      mbar_init(bar_kv_empty + 8 * s, 1);
+      mbar_init(bar_kv_empty + 8 * s, 2);  // one commit from each issuing warp
     }
     for (int w = 0; w < 2; ++w) {
       mbar_init(bar_s_full + 8 * w, 1);
@@ -488,6 +486,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_o_done + 8 * w, 1);
       mbar_init(bar_s_free + 8 * w, kBM);
     }
+
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -527,8 +526,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int slot = it % C::kStages;
             if (it >= C::kStages)
               ok = mbar_wait(bar_kv_empty + 8 * slot, ((it / C::kStages) + 1) & 1, abort_flag,
-                             a.status, 1, it);
+                             a.status, 1, it, a.wait_ns);
             if (!ok) break;
+            // test hook: stop feeding the ring so that a consumer's bounded wait runs out
+            if (a.stall_after >= 0 && it >= a.stall_after) {
+              ok = false;
+              break;
+            }
             mbar_expect_tx(bar_kv_full + 8 * slot, C::kTileBytes);
             const CUtensorMap* map = which == 0 ? &tmap_k : &tmap_v;
             for (int bx = 0; bx < C::kBoxes; ++bx)
@@ -538,124 +542,113 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp == 1) {
-    // -------------------------------------------------------------- MMA issuer ----
-    if (lane == 0 && n_tiles > 0) {
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------------------- MMA issuers ----
+    // One issuing warp per query tile (warp 1: tile 0, warp 2: tile 1). The two tiles are
+    // independent instruction streams, so a tile that is still in its exponentials never holds
+    // back the other one and the two softmax groups are free to run out of step (which is what
+    // keeps the exp unit busy: one group's loads, maxima and stores overlap the other group's
+    // exponentials). The whole warp runs the loop so that descriptors and loop state stay
+    // warp-uniform; the tcgen05.mma / tcgen05.commit instructions are executed by one elected
+    // lane. A K/V ring slot is released when both warps have committed their reads of it.
+    if (n_tiles > 0) {
+      const int w = warp - 1;
       constexpr unsigned kFmt = kBf16 ? 1u : 0u;
       constexpr unsigned idesc_s = make_idesc(kFmt, 0, kBN, kBM);
       constexpr unsigned idesc_pv = make_idesc(kFmt, 1, D, kBM);
-      const unsigned t_s[2] = {tmem_base + C::kColS0, tmem_base + C::kColS1};
-      const unsigned t_o[2] = {tmem_base + C::kColO0, tmem_base + C::kColO1};
-      [[maybe_unused]] const unsigned t_p[2] = {tmem_base + C::kColP0, tmem_base + C::kColP1};
-      // Descriptors are built once; inside the issue loops a descriptor is a base plus a
-      // compile-time constant in its 16-byte-unit address field, so the single issuing lane
-      // spends a couple of instructions per MMA.
-      const unsigned long long dq[2] = {desc_kmajor(s_q), desc_kmajor(s_q + C::kTileBytes)};
+      const unsigned t_s = tmem_base + (w == 0 ? C::kColS0 : C::kColS1);
+      const unsigned t_o = tmem_base + (w == 0 ? C::kColO0 : C::kColO1);
+      [[maybe_unused]] const unsigned t_p = tmem_base + (w == 0 ? C::kColP0 : C::kColP1);
+      const unsigned long long qd = desc_kmajor(s_q + w * C::kTileBytes);
+      [[maybe_unused]] const unsigned long long pd = desc_kmajor(s_p + w * C::kPBytes);
       const unsigned long long dkv0_k = desc_kmajor(s_kv);
       const unsigned long long dkv0_v = desc_mnmajor(s_kv, kBN * 128, 1024);
-      [[maybe_unused]] const unsigned long long dp[2] = {desc_kmajor(s_p),
-                                                         desc_kmajor(s_p + C::kPBytes)};
       constexpr unsigned kSlotUnits = C::kTileBytes >> 4;  // one ring slot in 16-byte units
-      auto issue_s = [&](int w, int slot) {
-        const unsigned long long qd = dq[w];
+      const unsigned b_s_full = bar_s_full + 8 * w, b_s_free = bar_s_free + 8 * w;
+      const unsigned b_p_full = bar_p_full + 8 * w, b_o_done = bar_o_done + 8 * w;
+      // S_w = Q_w K^T, then `then_bar` (and the slot's release) from the same elected lane
+      auto issue_s = [&](int slot) {
         const unsigned long long kd = dkv0_k + static_cast<unsigned long long>(slot * kSlotUnits);
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          constexpr unsigned kBox = (kBM * 128) >> 4;
-          const unsigned off = (ks / 4) * kBox + (ks % 4) * 2;  // 64-element box, 32 B per step
-          mma_ss(t_s[w], qd + off, kd + off, idesc_s, ks > 0 ? 1u : 0u);
-        }
-      };
-      auto issue_pv = [&](int w, int slot, bool acc) {
-        const unsigned long long vd = dkv0_v + static_cast<unsigned long long>(slot * kSlotUnits);
-#pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
-          const unsigned long long bd = vd + ks * (2048 >> 4);  // 16 keys = two 8-row groups
-          const unsigned accum = (acc || ks > 0) ? 1u : 0u;
-          if constexpr (kPInTmem) {
-            mma_ts(t_o[w], t_p[w] + ks * 8, bd, idesc_pv, accum);
-          } else {
+          for (int ks = 0; ks < D / 16; ++ks) {
             constexpr unsigned kBox = (kBM * 128) >> 4;
-            mma_ss(t_o[w], dp[w] + ((ks / 4) * kBox + (ks % 4) * 2), bd, idesc_pv, accum);
+            const unsigned off = (ks / 4) * kBox + (ks % 4) * 2;  // 64-element box, 32 B per step
+            mma_ss(t_s, qd + off, kd + off, idesc_s, ks > 0 ? 1u : 0u);
           }
         }
       };
-      bool ok = true;
-      // prologue: S_0(0), S_1(0)
-      ok = mbar_wait(bar_kv_full, 0, abort_flag, a.status, 2, 0);
-      for (int w = 0; w < 2 && ok; ++w) {
-        ok = mbar_wait(bar_q_full + 8 * w, 0, abort_flag, a.status, 3, w);
-        if (!ok) break;
-        tc_fence_after();
-        issue_s(w, 0);
-        tc_commit(bar_s_full + 8 * w);
-      }
-      if (ok) tc_commit(bar_kv_empty);
-      if constexpr (C::kEarlyS) {
-        // S_w(j+1) goes out as soon as the softmax threads hold S_w(j) in registers; PV_w(j)
-        // follows when P_w(j) is written. The tensor core works on the next scores while
-        // the exponentials of the current tile run.
-        for (int j = 0; j < n_tiles && ok; ++j) {
-          const int it_v = 2 * j + 1, it_k = 2 * j + 2;
-          const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
-          const bool more = j + 1 < n_tiles;
-          if (more) {
-            ok = mbar_wait(bar_kv_full + 8 * slot_k, (it_k / C::kStages) & 1, abort_flag,
-                           a.status, 5, j);
-            for (int w = 0; w < 2 && ok; ++w) {
-              ok = mbar_wait(bar_s_free + 8 * w, j & 1, abort_flag, a.status, 9, j);
-              if (!ok) break;
-              tc_fence_after();
-              issue_s(w, slot_k);
-              tc_commit(bar_s_full + 8 * w);
+      auto issue_pv = [&](int slot, bool acc) {
+        const unsigned long long vd = dkv0_v + static_cast<unsigned long long>(slot * kSlotUnits);
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < kBN / 16; ++ks) {
+            const unsigned long long bd = vd + ks * (2048 >> 4);  // 16 keys = two 8-row groups
+            const unsigned accum = (acc || ks > 0) ? 1u : 0u;
+            if constexpr (kPInTmem) {
+              mma_ts(t_o, t_p + ks * 8, bd, idesc_pv, accum);
+            } else {
+              constexpr unsigned kBox = (kBM * 128) >> 4;
+              mma_ss(t_o, pd + ((ks / 4) * kBox + (ks % 4) * 2), bd, idesc_pv, accum);
             }
-            if (ok) tc_commit(bar_kv_empty + 8 * slot_k);
           }
-          if (ok)
-            ok = mbar_wait(bar_kv_full + 8 * slot_v, (it_v / C::kStages) & 1, abort_flag,
-                           a.status, 4, j);
-          for (int w = 0; w < 2 && ok; ++w) {
-            RAB_TR(2, j, 3 * w);
-            ok = mbar_wait(bar_p_full + 8 * w, j & 1, abort_flag, a.status, 6, j);
-            RAB_TR(2, j, 3 * w + 1);
+        }
+      };
+      auto commit2 = [&](unsigned bar_a, unsigned bar_b) {
+        if (elect_one()) {
+          tc_commit(bar_a);
+          tc_commit(bar_b);
+        }
+      };
+      auto wait = [&](unsigned bar, unsigned parity, int which, int tile) {
+        return __all_sync(0xffffffffu,
+                          mbar_wait(bar, parity, abort_flag, a.status, which, tile, a.wait_ns)) != 0;
+      };
+      auto wait_kv = [&](int it, int which, int tile) {
+        return wait(bar_kv_full + 8 * (it % C::kStages), (it / C::kStages) & 1, which, tile);
+      };
+      // K_t is ring item 2t, V_t is item 2t+1
+      bool ok = wait_kv(0, 2, 0) && wait(bar_q_full + 8 * w, 0, 3, w);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        commit2(b_s_full, bar_kv_empty);
+      }
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int it_v = 2 * t + 1, it_k = 2 * t + 2;
+        const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
+        const bool more = t + 1 < n_tiles;
+        if constexpr (C::kEarlyS) {
+          // S_w(t+1) goes out as soon as the softmax threads hold S_w(t) in registers; P.V of
+          // tile t follows when its P is written. The tensor core works on the next scores
+          // while the exponentials of the current tile run.
+          if (more) {
+            ok = wait_kv(it_k, 5, t) && wait(b_s_free, t & 1, 9, t);
             if (!ok) break;
             tc_fence_after();
-            issue_pv(w, slot_v, j > 0);
-            tc_commit(bar_o_done + 8 * w);
-            RAB_TR(2, j, 3 * w + 2);
+            issue_s(slot_k);
+            commit2(b_s_full, bar_kv_empty + 8 * slot_k);
           }
-          if (ok) tc_commit(bar_kv_empty + 8 * slot_v);
-        }
-      } else {
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int it_v = 2 * j + 1, it_k = 2 * j + 2;
-        const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
-        const bool more = j + 1 < n_tiles;
-        ok = mbar_wait(bar_kv_full + 8 * slot_v, (it_v / C::kStages) & 1, abort_flag, a.status, 4,
-                       j);
-        if (ok && more)
-          ok = mbar_wait(bar_kv_full + 8 * slot_k, (it_k / C::kStages) & 1, abort_flag, a.status,
-                         5, j);
-        for (int w = 0; w < 2 && ok; ++w) {
-          RAB_TR(2, j, 3 * w);
-          ok = mbar_wait(bar_p_full + 8 * w, j & 1, abort_flag, a.status, 6, j);
-          RAB_TR(2, j, 3 * w + 1);
+          ok = wait_kv(it_v, 4, t) && wait(b_p_full, t & 1, 6, t);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(w, slot_v, j > 0);
+          issue_pv(slot_v, t > 0);
+          commit2(b_o_done, bar_kv_empty + 8 * slot_v);
+        } else {
+          // P aliases S: P.V of tile t and the scores of tile t+1 go out together once P_w(t)
+          // is written (the scores' completion tells the softmax group that P.V is done too).
+          ok = wait_kv(it_v, 4, t) && (!more || wait_kv(it_k, 5, t)) && wait(b_p_full, t & 1, 6, t);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(slot_v, t > 0);
           if (more) {
-            issue_s(w, slot_k);
-            tc_commit(bar_s_full + 8 * w);
+            issue_s(slot_k);
+            commit2(b_s_full, bar_kv_empty + 8 * slot_v);
+            if (elect_one()) tc_commit(bar_kv_empty + 8 * slot_k);
           } else {
-            tc_commit(bar_o_done + 8 * w);
+            commit2(b_o_done, bar_kv_empty + 8 * slot_v);
           }
-          RAB_TR(2, j, 3 * w + 2);
         }
-        if (ok) {
-          tc_commit(bar_kv_empty + 8 * slot_v);
-          if (more) tc_commit(bar_kv_empty + 8 * slot_k);
-        }
-      }
       }
     }
   }
@@ -675,8 +668,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const long long qdoc = a.doc_len > 0 ? qpos / a.doc_len : 0;
     const float scale_log2 = rsqrtf(static_cast<float>(DR)) * kLog2e;
 
-    float m_used = -INFINITY;  // reference point of P and O, log2 units
-    float m_true = -INFINITY;  // true running max, log2 units
+    float m_ref = -INFINITY;  // reference point of P, O and l, log2 units (see the tile loop)
     float l_run = 0.f;
     bool ok = true;
 
@@ -712,9 +704,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (c_hi < c_lo) c_hi = c_lo;
         const bool full = __all_sync(0xffffffffu, c_lo == 0 && c_hi == kBN);
 
-        RAB_TR(w, j, 0);
-        ok = mbar_wait(bar_s_full + 8 * w, j & 1, abort_flag, a.status, 7, j);
-        RAB_TR(w, j, 1);
+        ok = mbar_wait(bar_s_full + 8 * w, j & 1, abort_flag, a.status, 7, j, a.wait_ns);
         ok = __all_sync(0xffffffffu, ok);  // the tensor-memory accesses below are warp-collective
         if (!ok) break;
         tc_fence_after();
@@ -727,9 +717,87 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc_fence_before();
           mbar_arrive(bar_s_free + 8 * w);
         }
-        RAB_TR(w, j, 2);
-        float mx = -INFINITY;
-        if (full) {
+        if (!full) {
+          // hidden columns become -inf, which the exponential below turns into exactly 0
+#pragma unroll
+          for (int i = 0; i < kBN; ++i) s[i] = (i >= c_lo && i < c_hi) ? s[i] : -INFINITY;
+        }
+
+        // P = 2^(s * scale - m_ref), two columns at a time (packed fp32x2 multiply-add and add),
+        // row sum in two independent accumulators, 16-bit P for the second MMA. m_ref is the
+        // row's reference point: the row maximum at the time it was last set. It is NOT moved on
+        // every tile: as long as the row sum of a tile stays below 2^15 every P fits 16 bits and
+        // the fp32 sums hold it, so the common tile costs no row maximum at all (64 three-input
+        // max instructions per row saved) and no rescale of O. A tile whose sum runs over (some
+        // score more than 2^15 above the reference), or the first tile a row sees, takes the
+        // slow path below: true row maximum, new reference, O and l rescaled, P recomputed.
+        // P is produced and stored in two halves of 64 keys so that only 32 packed registers
+        // are live beside the 128 scores.
+        const float2 scale2 = make_float2(scale_log2, scale_log2);
+        float2 sum_a, sum_b;
+        auto half_tile = [&](int h, float neg_m) {
+          const float2 negm2 = make_float2(neg_m, neg_m);
+          unsigned pk[kBN / 4];
+#pragma unroll
+          for (int i = 0; i < kBN / 2; i += 4) {
+            const int c = h * (kBN / 2) + i;
+            const float2 x0 = ffma2(make_float2(s[c], s[c + 1]), scale2, negm2);
+            const float2 x1 = ffma2(make_float2(s[c + 2], s[c + 3]), scale2, negm2);
+            const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
+            const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
+            sum_a = fadd2(sum_a, p0);
+            sum_b = fadd2(sum_b, p1);
+            pk[i / 2] = pack16<kBf16>(p0.x, p0.y);
+            pk[i / 2 + 1] = pack16<kBf16>(p1.x, p1.y);
+          }
+          if constexpr (kPInTmem) {
+            // keys 64h .. 64h+63 as 32 packed columns (over the consumed S columns when P aliases S)
+            tmem_st32u(t_p + h * 32, &pk[0]);
+          } else {
+            // K-major 128B-swizzled P tile: row r, 16-byte piece q of 64-key box h at
+            // h * 16 KiB + r * 128 + ((q ^ (r & 7)) * 16)
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece) {
+              const unsigned box = s_p + w * C::kPBytes + h * (kBM * 128) + row * 128;
+              const unsigned addr = box + ((piece ^ (row & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                           "r"(pk[4 * piece]), "r"(pk[4 * piece + 1]), "r"(pk[4 * piece + 2]),
+                           "r"(pk[4 * piece + 3])
+                           : "memory");
+            }
+          }
+        };
+        // P_w(j-1) must have been consumed (and O_w must be at rest) before P_w(j) is written or
+        // O_w rescaled: wait for PV_w(j-1), issued a whole softmax ago. (With P aliased over S
+        // the completed S_w(j) already implies it.)
+        auto wait_prev_pv = [&]() {
+          if constexpr (C::kEarlyS) {
+            if (j > 0) {
+              ok = mbar_wait(bar_o_done + 8 * w, (j - 1) & 1, abort_flag, a.status, 10, j, a.wait_ns);
+              ok = __all_sync(0xffffffffu, ok);
+              if (ok) tc_fence_after();
+            }
+          }
+        };
+        // a row without a reference yet needs one as soon as it sees a key
+        bool slow = __any_sync(0xffffffffu, m_ref == -INFINITY && c_hi > c_lo) != 0;
+        float row_sum = 0.f;
+        if (!slow) {
+          const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+          sum_a = make_float2(0.f, 0.f);
+          sum_b = make_float2(0.f, 0.f);
+          wait_prev_pv();
+          if (!ok) break;
+          half_tile(0, neg_m);
+          half_tile(1, neg_m);
+          row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+          slow = __any_sync(0xffffffffu, !(row_sum <= kRowSumLimit)) != 0;  // also catches NaN
+        }
+        else {
+          wait_prev_pv();
+          if (!ok) break;
+        }
+        if (slow) {
           float m0 = s[0], m1 = s[1], m2 = s[2], m3 = s[3];  // four independent chains
 #pragma unroll
           for (int i = 4; i < kBN; i += 8) {
@@ -740,103 +808,34 @@ __global__ void __launch_bounds__(kThreads, 1)
               m3 = max3(m3, s[i + 6], s[i + 7]);
             }
           }
-          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-        } else {
-          // hidden columns become -inf, which the exponential below turns into exactly 0
-#pragma unroll
-          for (int i = 0; i < kBN; ++i) {
-            s[i] = (i >= c_lo && i < c_hi) ? s[i] : -INFINITY;
-            mx = fmaxf(mx, s[i]);
+          const float tile_max = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * scale_log2;  // -inf stays -inf
+          float alpha = 1.f;
+          bool rescale = false;
+          if (tile_max > m_ref) {
+            if (m_ref > -INFINITY) {
+              alpha = ex2(m_ref - tile_max);
+              rescale = true;
+            }
+            m_ref = tile_max;
           }
-        }
-        RAB_TR(w, j, 6);
-        const float tile_max = mx * scale_log2;  // -inf stays -inf (scale > 0)
-        m_true = fmaxf(m_true, tile_max);
-        // Move the reference point only when it is unset or the max moved by more than the
-        // threshold; otherwise P just runs a little above 1 (at most 2^8), which 16-bit P and
-        // the fp32 sums hold without trouble.
-        float alpha = 1.f;
-        bool rescale = false;
-        if (m_true > m_used + kRescaleThreshold || (m_used == -INFINITY && m_true > -INFINITY)) {
-          if (m_used > -INFINITY) {
-            alpha = ex2(m_used - m_true);
-            rescale = true;
-          }
-          m_used = m_true;
-        }
-        if constexpr (C::kEarlyS) {
-          // P_w(j-1) must have been consumed (and O_w must be at rest) before P_w(j) is
-          // written or O_w rescaled: wait for PV_w(j-1). It was issued a whole softmax ago.
-          if (j > 0) {
-            ok = mbar_wait(bar_o_done + 8 * w, (j - 1) & 1, abort_flag, a.status, 10, j);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-          }
-        }
-        RAB_TR(w, j, 7);
-        const bool do_rescale = j > 0 && __any_sync(0xffffffffu, rescale);
-        if (do_rescale) {
-          // O_w is at rest here: PV_w(j-1) has completed (aliased P: S_w(j) was issued after
-          // it and has completed; separate P: waited for just above).
-          l_run *= alpha;
+          if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+            // O_w is at rest here: PV_w(j-1) has completed
+            l_run *= alpha;
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            float o[32];
-            tmem_ld32(t_o + c * 32, o);
+            for (int c = 0; c < D / 32; ++c) {
+              float o[32];
+              tmem_ld32(t_o + c * 32, o);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st32(t_o + c * 32, o);
+              for (int i = 0; i < 32; ++i) o[i] *= alpha;
+              tmem_st32(t_o + c * 32, o);
+            }
           }
-        }
-        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-        RAB_TR(w, j, 3);
-
-        // P = 2^(s * scale - m_used) two columns at a time (packed fp32x2 multiply-add and
-        // add), row sum in two independent accumulators, 16-bit P for the second MMA.
-        const float2 scale2 = make_float2(scale_log2, scale_log2);
-        const float2 negm2 = make_float2(neg_m, neg_m);
-        float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-        unsigned pk[kBN / 2];
-#pragma unroll
-        for (int i = 0; i < kBN; i += 4) {
-          const float2 x0 = ffma2(make_float2(s[i], s[i + 1]), scale2, negm2);
-          const float2 x1 = ffma2(make_float2(s[i + 2], s[i + 3]), scale2, negm2);
-          const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
-          // Optionally (kPolyNum of every kPolyDen pairs of this stream) the exponential is
-          // computed on the FMA pipe instead of the exp unit. Off by default: measured on
-          // B200 it does not pay, because with the exp unit relieved the chain of the single
-          // MMA-issuing lane (wait, issue, complete, wake) bounds the tile period at about the
-          // same length.
-          float2 p1;
-          if ((i / 4) % kPolyDen < kPolyNum) {
-            p1 = exp2_poly2(x1);
-          } else {
-            p1 = make_float2(ex2(x1.x), ex2(x1.y));
-          }
-          sum_a = fadd2(sum_a, p0);
-          sum_b = fadd2(sum_b, p1);
-          pk[i / 2] = pack16<kBf16>(p0.x, p0.y);
-          pk[i / 2 + 1] = pack16<kBf16>(p1.x, p1.y);
-        }
-        const float row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-        RAB_TR(w, j, 4);
-        if constexpr (kPInTmem) {
-          // keys 0..127 as 64 packed columns (over the consumed S columns when P aliases S)
-          tmem_st32u(t_p, &pk[0]);
-          tmem_st32u(t_p + 32, &pk[32]);
-        } else {
-          // K-major 128B-swizzled P tile: row r, 16-byte piece q of a 64-key box at
-          // r * 128 + ((q ^ (r & 7)) * 16)
-#pragma unroll
-          for (int piece = 0; piece < 16; ++piece) {
-            const unsigned box = s_p + w * C::kPBytes + (piece / 8) * (kBM * 128) + row * 128;
-            const unsigned addr = box + (((piece & 7) ^ (row & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
-                         "r"(pk[4 * piece]), "r"(pk[4 * piece + 1]), "r"(pk[4 * piece + 2]),
-                         "r"(pk[4 * piece + 3])
-                         : "memory");
-          }
+          const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+          sum_a = make_float2(0.f, 0.f);
+          sum_b = make_float2(0.f, 0.f);
+          half_tile(0, neg_m);
+          half_tile(1, neg_m);
+          row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         }
         l_run += row_sum;
         if constexpr (kPInTmem) {
@@ -847,33 +846,30 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tc_fence_before();
         mbar_arrive(bar_p_full + 8 * w);
-        RAB_TR(w, j, 5);
       }
     }
 
     // ---------------------------------------------------------------- epilogue ----
     if (ok && n_tiles > 0)
       ok = mbar_wait(bar_o_done + 8 * w, C::kEarlyS ? ((n_tiles - 1) & 1) : 0, abort_flag, a.status,
-                     8, n_tiles);
+                     8, n_tiles, a.wait_ns);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
       const size_t grow = (static_cast<size_t>(bh) * a.Sq + static_cast<size_t>(sq) * q_seg_len +
                            (row_valid ? r_in_seg : 0));
       float* o_g = a.out + grow * DR;
-      // (the polynomial exponential turns a hidden score into 2^-125, not 0, so "saw a key"
-      // is read off the running maximum, not off the sum)
-      const bool have = row_valid && n_tiles > 0 && m_true > -INFINITY;
+      const bool have = row_valid && n_tiles > 0 && m_ref > -INFINITY;
       float m_old = -INFINITY, l_old = 0.f;
       if (!fresh && row_valid) {
         m_old = a.m[grow];
         l_old = a.l[grow];
       }
-      const float m_new = have ? m_true * kLn2 : -INFINITY;  // natural-log units
+      const float m_new = have ? m_ref * kLn2 : -INFINITY;  // natural-log units
       const float m_fin = fmaxf(m_old, m_new);
       const float ca = (m_old == -INFINITY) ? 0.f : expf(m_old - m_fin);
-      // O and l are relative to m_used; bring them to m_fin
-      const float cb = have ? ex2(m_used - m_true) * expf(m_new - m_fin) : 0.f;
+      // O and l are relative to m_ref; bring them to m_fin
+      const float cb = have ? expf(m_new - m_fin) : 0.f;
       const float l_fin = ca * l_old + cb * l_run;
       const float inv = finalize ? (l_fin > 0.f ? 1.f / l_fin : 0.f) : 1.f;
       // a row that saw nothing keeps its state unless the caller asked to overwrite / normalise
@@ -968,7 +964,9 @@ int make_map(CUtensorMap* map, int dtype, const void* base, int D, long long row
   return RA_OK;
 }
 
-int g_p_in_tmem = 1;  // which P path the launcher uses (both are kept buildable and tested)
+// Test hooks (see ra_debug_set_wait_limit_ns / ra_debug_stall_producer_after).
+std::atomic<unsigned long long> g_wait_ns{kWaitLimitNs};
+std::atomic<int> g_stall_after{-1};
 
 template <int D, bool kBf16, bool kPInTmem, int DR>
 int launch_cfg(const StepArgs& a, cudaStream_t stream) {
@@ -1001,6 +999,8 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.flags = a.flags;
   t.doc_len = a.doc_len;
   t.status = a.status;
+  t.wait_ns = g_wait_ns.load(std::memory_order_relaxed);
+  t.stall_after = g_stall_after.load(std::memory_order_relaxed);
   const long long n_qblocks = static_cast<long long>(t.n_qblocks_per_seg) * a.qmap.n_seg;
   RAB_REQUIRE(n_qblocks <= 65535, RA_ERR_INVALID, "attention step: too many query blocks (%lld)",
               n_qblocks);
@@ -1014,20 +1014,23 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
 
 template <int D>
 int launch_d(int dtype, const StepArgs& a, cudaStream_t stream) {
+  // P stays in tensor memory unless the caller asks for the shared-memory path (kept as a
+  // cross-check of the first one; both are tested)
+  const bool p_in_tmem = (a.flags & RA_STEP_P_IN_SMEM) == 0;
   // the 64-wide kernel also takes head_dim 32 (DR = 32)
   if constexpr (D == 64) {
     if (a.D == 32) {
       if (dtype == RA_BF16)
-        return g_p_in_tmem ? launch_cfg<64, true, true, 32>(a, stream)
-                           : launch_cfg<64, true, false, 32>(a, stream);
-      return g_p_in_tmem ? launch_cfg<64, false, true, 32>(a, stream)
-                         : launch_cfg<64, false, false, 32>(a, stream);
+        return p_in_tmem ? launch_cfg<64, true, true, 32>(a, stream)
+                         : launch_cfg<64, true, false, 32>(a, stream);
+      return p_in_tmem ? launch_cfg<64, false, true, 32>(a, stream)
+                       : launch_cfg<64, false, false, 32>(a, stream);
     }
   }
   if (dtype == RA_BF16) {
-    return g_p_in_tmem ? launch_cfg<D, true, true, D>(a, stream) : launch_cfg<D, true, false, D>(a, stream);
+    return p_in_tmem ? launch_cfg<D, true, true, D>(a, stream) : launch_cfg<D, true, false, D>(a, stream);
   }
-  return g_p_in_tmem ? launch_cfg<D, false, true, D>(a, stream) : launch_cfg<D, false, false, D>(a, stream);
+  return p_in_tmem ? launch_cfg<D, false, true, D>(a, stream) : launch_cfg<D, false, false, D>(a, stream);
 }
 
 }  // namespace
@@ -1051,19 +1054,12 @@ int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream) {
   return launch_d<128>(dtype, a, stream);
 }
 
-#ifdef RAB_TRACE
-int read_trace(long long* out) {
-  RAB_CUDA(cudaDeviceSynchronize());
-  RAB_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 3 * 64 * 8));
-  return RA_OK;
-}
-#endif
 
-void set_tc_p_in_tmem(int on) { g_p_in_tmem = on ? 1 : 0; }
+void set_tc_wait_limit_ns(unsigned long long ns) {
+  g_wait_ns.store(ns ? ns : kWaitLimitNs, std::memory_order_relaxed);
+}
+void set_tc_stall_after(int items) { g_stall_after.store(items, std::memory_order_relaxed); }
 
 
 }  // namespace rab
 
-#ifdef RAB_TRACE
-extern "C" RA_API int ra_debug_read_trace(long long* out) { return rab::read_trace(out); }
-#endif

@@ -107,3 +107,50 @@ def test_prefill_on_host_buffers(dtype):
     tol = 1e-5 if dtype == torch.float32 else 1e-3
     assert_close(out.numpy(), want, tol, tol, "out")
     assert_close(lse.numpy(), want_lse, tol, tol, "lse")
+
+
+def _small_causal_case(seed=3, S=1024, D=64, H=2):
+    q, k, v = normal_inputs(seed, 1, H, H, S, S, D)
+    q, k, v = (round_to(x, torch.float16) for x in (q, k, v))
+    return q, k, v, oracle.cpu_attention(q, k, v, True)
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable():
+    """The tcgen05 kernel's waits are bounded: with the TMA producer told to stop after the
+    first K/V tiles and the limit set to a few milliseconds, the kernel returns by itself, the
+    status word says which wait gave up, host entry points that synchronise report
+    RA_ERR_DEVICE_WAIT, and after the word is read (which clears it) the same launch is right."""
+    from ring_attention_b200._lib import RingAttentionError, lib
+    L = lib()
+    S, D, H = 1024, 64, 2
+    q, k, v, want = _small_causal_case(S=S, D=D, H=H)
+    dq, dk, dv = (dev(x, torch.float16) for x in (q, k, v))
+    out = torch.zeros((1, H, S, D), device="cuda")
+    m = torch.zeros((1, H, S), device="cuda")
+    l = torch.zeros_like(m)
+    one = SegMap.make([0], S)
+    shape = api.AttentionShape(1, H, S, S, D)
+    assert api.device_status()[0] == 0
+    L.ra_debug_set_wait_limit_ns(5_000_000)
+    L.ra_debug_stall_producer_after(2)
+    try:
+        api.attention_step_ex(dq, dk, dv, out, m, l, shape, one, one, causal=True, fresh=True, finalize=True)
+        torch.cuda.synchronize()  # returns: nothing waits forever
+        # a host-buffer entry point synchronises, so it reports the failure itself
+        hq, hk, hv = (torch.from_numpy(x).to(torch.float16).pin_memory() for x in (q, k, v))
+        hout = torch.empty((1, H, S, D)).pin_memory()
+        with pytest.raises(RingAttentionError) as err:
+            api.check(L.ra_prefill_host(api.RA_F16, hq.data_ptr(), hk.data_ptr(), hv.data_ptr(),
+                                        hout.data_ptr(), None, shape.c(), one, one, 1,
+                                        api.RA_STEP_CAUSAL, 0))
+        assert err.value.code == 5  # RA_ERR_DEVICE_WAIT
+    finally:
+        L.ra_debug_stall_producer_after(-1)
+        L.ra_debug_set_wait_limit_ns(0)
+    status = api.device_status()  # reads and clears
+    assert status[0] == 5 and status[1] > 0, status
+    assert api.device_status()[0] == 0
+    api.attention_step_ex(dq, dk, dv, out, m, l, shape, one, one, causal=True, fresh=True, finalize=True)
+    torch.cuda.synchronize()
+    assert api.device_status()[0] == 0
+    assert_close(out.cpu().numpy(), want, 1e-3, 1e-3, "after the status word was cleared")

@@ -103,13 +103,14 @@ def test_config1_fp32_noncausal_mha_output_and_lse():
     assert_close(lse, want_lse, 1e-5, 1e-5, "lse")
 
 
-def run_ex(q, k, v, qmap, kmap, stride, causal, dtype, kvH, doc_len=0, force_simt=False):
+def run_ex(q, k, v, qmap, kmap, stride, causal, dtype, kvH, doc_len=0, force_simt=False,
+           p_in_smem=False):
     B, H, Sq, D = q.shape
     out, m, l = state(B, H, Sq, D, poison=True)
     api.attention_step_ex(dev(q, dtype), dev(k, dtype), dev(v, dtype), out, m, l,
                           api.AttentionShape(B, H, Sq, k.shape[2], D, kvH), qmap, kmap, stride,
                           causal=causal, fresh=True, finalize=True, doc_len=doc_len,
-                          force_simt=force_simt)
+                          force_simt=force_simt, p_in_smem=p_in_smem)
     torch.cuda.synchronize()
     assert api.device_status()[0] == 0
     return out.cpu().numpy(), api.attention_lse(m, l).cpu().numpy()
@@ -198,20 +199,15 @@ def test_ragged_shapes_fp16(shape, causal):
     assert_close(got, want, 1e-3, 1e-3, "out")
 
 
-@pytest.mark.parametrize("p_in_tmem", [1, 0])
-def test_both_p_paths_of_the_tensor_core_kernel(p_in_tmem):
-    from ring_attention_b200._lib import lib
-    lib().ra_debug_set_p_in_tmem(p_in_tmem)
-    try:
-        for D in (64, 128):
-            q, k, v = normal_inputs(30 + D, 1, 2, 2, 384, 640, D)
-            q, k, v = (round_to(x, torch.float16) for x in (q, k, v))
-            want = oracle.cpu_attention(q, k, v, True, kv_heads=2)
-            qmap, kmap = SegMap.make([640 - 384], 384), SegMap.make([0], 640)
-            got, _ = run_ex(q, k, v, qmap, kmap, 1, True, torch.float16, 2)
-            assert_close(got, want, 1e-3, 1e-3, f"D={D}")
-    finally:
-        lib().ra_debug_set_p_in_tmem(1)
+@pytest.mark.parametrize("p_in_smem", [False, True])
+def test_both_p_paths_of_the_tensor_core_kernel(p_in_smem):
+    for D in (32, 64, 128):
+        q, k, v = normal_inputs(30 + D, 1, 2, 2, 384, 1664, D)
+        q, k, v = (round_to(x, torch.float16) for x in (q, k, v))
+        want = oracle.cpu_attention(q, k, v, True, kv_heads=2)
+        qmap, kmap = SegMap.make([1664 - 384], 384), SegMap.make([0], 1664)
+        got, _ = run_ex(q, k, v, qmap, kmap, 1, True, torch.float16, 2, p_in_smem=p_in_smem)
+        assert_close(got, want, 1e-3, 1e-3, f"D={D}")
 
 
 def test_rows_without_visible_keys_keep_their_state():
