@@ -59,6 +59,10 @@ WORKLOADS = {
 LAYOUTS = {"contiguous": 0, "zigzag": 1, "striped": 2}
 DECODE = dict(batch=4, heads=32, kv_heads=8, head_dim=128, prompt=262144, dtype="fp16")
 METRIC = "causal-adjusted attention TFLOP/s (prefill, whole job)"
+# DRAM bytes (read + write) of one step-kernel launch on the benchmark shape at N = 1, from one ncu
+# capture of that launch (179.5 MB read + 35.6 MB written; algorithmic: 100.7 MB of Q/K/V in, 68.2 MB
+# of out / m / l). A property of the workload: the run that prints it does not re-measure it.
+TRAFFIC_CONFIG2_N1 = 215.0e6
 
 
 def causal_flops(B, H, S, D):
@@ -86,7 +90,6 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.lines = []
-        self.t_mark = 0.0
 
     def start(self):
         try:
@@ -105,22 +108,19 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append((time.perf_counter(), line.strip()))
 
-    def mark(self):
-        """Samples from here on are the ones taken during the timed regions."""
-        self.t_mark = time.perf_counter()
+    def now(self):
+        return time.perf_counter()
 
-    def stop(self):
+    def window(self, t0, t1):
+        """Clocks and throttle reasons of the samples taken between two perf_counter stamps
+        (all samples when the window caught none: a timed region shorter than the sampling period)."""
         if not self.proc:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        self.proc.terminate()  # the exact process started above
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            pass
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        timed = [ln for t, ln in self.lines if t >= self.t_mark]
-        for ln in (timed if timed else [ln for _, ln in self.lines]):
+        lines = list(self.lines)
+        timed = [ln for t, ln in lines if t0 <= t <= t1]
+        for ln in (timed if timed else [ln for _, ln in lines]):
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -133,7 +133,16 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    samples=len(sm), reasons=sorted(reasons))
+                    samples=len(sm), in_window=bool(timed), reasons=sorted(reasons))
+
+    def stop(self):
+        if not self.proc:
+            return
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
 
 
 # ------------------------------------------------------------------ CPU reference arm ----
@@ -201,12 +210,119 @@ def run_reference_arm(args):
 
 # ------------------------------------------------------------------------- GPU arm ----
 
+class Case:
+    """One prefill workload materialised on this rank: shards, partition, output buffer."""
+
+    def __init__(self, api, torch, name, P, rank, dev, want_host):
+        w = dict(WORKLOADS[name])
+        if w["seq"] is None:
+            w["seq"] = w["seq_per_gpu"] * P
+        self.key, self.w, self.P, self.rank = name, w, P, rank
+        B, H, kvH, S, D = w["batch"], w["heads"], w["kv_heads"], w["seq"], w["head_dim"]
+        self.layout = LAYOUTS[w["layout"]]
+        self.doc_len = S // 4 if w["doc_len"] == "seq/4" else int(w["doc_len"])
+        w["doc_len"] = self.doc_len
+        self.part = api.RingPartition(P, rank, S, self.layout, w["n_splits"])
+        self.rows = self.part.local_positions()
+        sloc = len(self.rows)
+        self.host = None
+        if name == "config2":
+            # Synthetic N(0,1) inputs, one seeded generator for the global tensors; each rank keeps its rows.
+            g = torch.Generator(device="cpu").manual_seed(42)
+            host = [torch.randn((B, H, S, D), generator=g).to(torch.float16)[:, :, self.rows].contiguous()
+                    for _ in range(3)]
+            self.host = [t.pin_memory() for t in host] if want_host else None
+            self.dq, self.dk, self.dv = (t.to(dev) for t in host)
+        else:
+            # The larger workloads generate each rank's shard on its GPU (same distribution, seed + rank),
+            # one (batch, head) slice at a time: materialising the global tensors on the host would take
+            # tens of GB, and a whole fp32 shard on the device several more.
+            g = torch.Generator(device=dev).manual_seed(42 + rank)
+
+            def gen(heads):
+                t = torch.empty((B, heads, sloc, D), dtype=torch.float16, device=dev)
+                for b in range(B):
+                    for h in range(heads):
+                        t[b, h] = (torch.randn((sloc, D), generator=g, device=dev) * w["scale"]).to(torch.float16)
+                return t
+            self.dq, self.dk, self.dv = gen(H), gen(kvH), gen(kvH)
+        self.out = torch.empty((B, H, sloc, D), dtype=torch.float32, device=dev)
+        # causal-adjusted FLOPs; with documents the mask is block-diagonal causal (per document)
+        self.flops = (causal_flops(B, H, S, D) if not self.doc_len
+                      else (S // self.doc_len) * causal_flops(B, H, self.doc_len, D))
+
+    def release(self):
+        self.dq = self.dk = self.dv = self.out = self.host = None
+
+
+def time_case(api, torch, dist, case, ring, schedule, K, W, world, dev, flush, sampler):
+    """W warm-up passes, then K passes timed with CUDA events on the launching stream (L2 flushed
+    between them, ranks aligned by a stream-ordered all-reduce that does not block the host),
+    bracketed by barrier + synchronize; then one pass with the driver's own event timings."""
+    w, S = case.w, case.w["seq"]
+    stream = torch.cuda.current_stream()
+    token = torch.zeros(1, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_pass(timed=False):
+        return ring.prefill(case.dq, case.dk, case.dv, seq=S, causal=True, layout=case.layout,
+                            n_splits=w["n_splits"], doc_len=case.doc_len, out=case.out, schedule=schedule,
+                            timed=timed)
+
+    for _ in range(W):
+        flush.fill_(1)
+        one_pass()
+    barrier()
+    assert api.device_status()[0] == 0, "a device-side wait ran out during warm-up"
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    barrier()
+    t_begin = sampler.now()
+    for i in range(K):
+        flush.fill_(i & 1)  # evict L2 between timed iterations (not timed)
+        if world > 1:
+            dist.all_reduce(token)  # aligns the ranks on the device; the host runs ahead
+        ev[i][0].record(stream)
+        one_pass()
+        ev[i][1].record(stream)
+    barrier()
+    t_end = sampler.now()
+    ms = sum(a.elapsed_time(b) for a, b in ev) / K
+    # one more pass with the driver's own event timings (the reference's RingResult fields):
+    # compute = sum of the step kernels, comm = sum of the transfers on the side stream,
+    # wait = pass time the compute stream spent not computing (transfers that were not hidden)
+    _, rt = one_pass(timed=True)
+    times = [ms, rt.total_ms, rt.comp_ms, rt.comm_ms, rt.wait_ms]
+    if world > 1:
+        t = torch.tensor(times, device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times = [float(x) for x in t]
+    clocks = sampler.window(t_begin, t_end)
+    return times, clocks
+
+
+def case_report(case, times, clocks, peaks, plan, checked):
+    """The figures of one workload (used for the secondary objects of the line)."""
+    ms = times[0]
+    value = case.flops / (ms * 1e-3) / 1e12
+    per_gpu = value / case.P
+    return {"workload": case.w["name"], "seq": case.w["seq"], "cp_size": case.P, "ms_per_step": ms,
+            "value": value, "unit": "TFLOP/s", "per_gpu_tflops": per_gpu,
+            "frac_burst": per_gpu / peaks["tflops"], "frac_sustained": per_gpu / peaks["tflops_sustained"],
+            "ring": {"total_ms": times[1], "comp_ms": times[2], "comm_ms": times[3], "wait_ms": times[4],
+                     "exposed_comm_frac": times[4] / max(times[1], 1e-9), "schedule": plan[0],
+                     "key_parts": plan[1], "kernel_launches_per_pass": plan[2]},
+            "checked_rows": checked, "clocks": clocks}
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
 
     from ring_attention_b200 import api
-    from ring_attention_b200._lib import SegMap
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -220,96 +336,49 @@ def run_gpu_arm(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     P = world
-    w = dict(WORKLOADS[args.workload])
-    if w["seq"] is None:
-        w["seq"] = w["seq_per_gpu"] * P
-    B, H, kvH, S, D = w["batch"], w["heads"], w["kv_heads"], w["seq"], w["head_dim"]
-    layout = LAYOUTS[w["layout"]]
-    doc_len = S // 4 if w["doc_len"] == "seq/4" else int(w["doc_len"])
-    w["doc_len"] = doc_len
-    part = api.RingPartition(P, rank, S, layout, w["n_splits"])
-    rows = part.local_positions()
-    sloc = len(rows)
-
-    if args.workload == "config2":
-        # Synthetic N(0,1) inputs, one seeded generator for the global tensors; each rank keeps its rows.
-        g = torch.Generator(device="cpu").manual_seed(42)
-        host = [torch.randn((B, H, S, D), generator=g).to(torch.float16)[:, :, rows].contiguous().pin_memory()
-                for _ in range(3)]
-        dq, dk, dv = (t.to(dev, non_blocking=True) for t in host)
-    else:
-        # The larger workloads generate each rank's shard on its GPU (same distribution, seed + rank);
-        # materialising the global tensors on the host would take tens of GB.
-        g = torch.Generator(device=dev).manual_seed(42 + rank)
-        dq = (torch.randn((B, H, sloc, D), generator=g, device=dev) * w["scale"]).to(torch.float16)
-        dk = (torch.randn((B, kvH, sloc, D), generator=g, device=dev) * w["scale"]).to(torch.float16)
-        dv = (torch.randn((B, kvH, sloc, D), generator=g, device=dev) * w["scale"]).to(torch.float16)
-        host = [t.cpu().pin_memory() for t in (dq, dk, dv)]
-    out = torch.empty((B, H, sloc, D), dtype=torch.float32, device=dev)
-    host_out = torch.empty((B, H, sloc, D), dtype=torch.float32).pin_memory()
+    peaks = measured_peaks()
     ring = api.Ring(rank, P)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
-    stream = torch.cuda.current_stream()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to start: begin before the warm-up
+    K, W = max(1, args.steps), max(args.warmup, 3)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def one_pass():
-        ring.prefill(dq, dk, dv, seq=S, causal=True, layout=layout, n_splits=w["n_splits"], doc_len=doc_len,
-                     out=out, schedule=args.schedule)
+    def plan_of(case):
+        w = case.w
+        return ring.plan(batch=w["batch"], heads=w["heads"], kv_heads=w["kv_heads"], seq=w["seq"],
+                         head_dim=w["head_dim"], causal=True, layout=case.layout, n_splits=w["n_splits"],
+                         doc_len=case.doc_len, schedule=args.schedule)
 
-    qmap1 = kmap1 = None
-    stride1 = 1
+    # ---- the benchmark line: the workload the metric is quoted on (or --workload) ----
+    case = Case(api, torch, args.workload, P, rank, dev, want_host=True)
+    w = case.w
+    B, H, kvH, S, D = w["batch"], w["heads"], w["kv_heads"], w["seq"], w["head_dim"]
+    times, clocks = time_case(api, torch, dist, case, ring, args.schedule, K, W, world, dev, flush, sampler)
+    ms = times[0]
+    plan = plan_of(case)
+
+    # end to end: this rank's shards in pinned host memory in, host result out, through the
+    # host-buffer entry points of the C ABI (copies inside the timed region)
+    host = case.host if case.host is not None else [t.cpu().pin_memory() for t in (case.dq, case.dk, case.dv)]
+    host_out = torch.empty(tuple(case.out.shape), dtype=torch.float32).pin_memory()
     if P == 1:
-        qmap1, kmap1, stride1 = part.step_maps(0)
+        qmap1, kmap1, stride1 = case.part.step_maps(0)
 
-    def one_pass_host():
-        if P == 1:
-            # the host-buffer entry point of the C ABI: upload, step, download, synchronise
+        def one_pass_host():
             api.check(api.lib().ra_prefill_host(
                 api.RA_F16, host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), host_out.data_ptr(),
                 None, api.AttentionShape(B, H, S, S, D, kvH).c(), qmap1, kmap1, stride1, api.RA_STEP_CAUSAL,
-                doc_len))
-        else:
-            dq.copy_(host[0], non_blocking=True)
-            dk.copy_(host[1], non_blocking=True)
-            dv.copy_(host[2], non_blocking=True)
-            one_pass()
-            host_out.copy_(out, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()  # nvidia-smi needs a moment to start: begin before the warm-up
-    for _ in range(max(args.warmup, 3)):
-        flush.fill_(1)
-        one_pass()
-    barrier()
-    assert api.device_status()[0] == 0, "a device-side wait ran out during warm-up"
-    K = max(1, args.steps)
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    barrier()
-    sampler.mark()
-    for i in range(K):
-        flush.fill_(i & 1)  # evict L2 between timed iterations (not timed)
-        if world > 1:
-            dist.barrier()
-        ev[i][0].record(stream)
-        one_pass()
-        ev[i][1].record(stream)
-    barrier()
-    ms_steps = [a.elapsed_time(b) for a, b in ev]
-    ms = sum(ms_steps) / K
-    # one more pass with the driver's own event timings (the reference's RingResult fields):
-    # compute = sum of the step kernels, comm = sum of the send/recv groups on the side stream,
-    # wait = pass time the compute stream spent not computing (transfers that were not hidden)
-    _, ring_t = ring.prefill(dq, dk, dv, seq=S, causal=True, layout=layout, n_splits=w["n_splits"],
-                             doc_len=doc_len, out=out, timed=True, schedule=args.schedule)
-    ring_times = [ring_t.total_ms, ring_t.comp_ms, ring_t.comm_ms, ring_t.wait_ms]
-
-    # end to end: host buffers in, host result out, copies inside the timed region
+                case.doc_len))
+    else:
+        def one_pass_host():
+            ring.prefill_host(host[0], host[1], host[2], host_out, seq=S, causal=True, layout=case.layout,
+                              n_splits=w["n_splits"], doc_len=case.doc_len, schedule=args.schedule)
     for _ in range(2):
         one_pass_host()
     barrier()
@@ -318,73 +387,82 @@ def run_gpu_arm(args):
         one_pass_host()
     barrier()
     ms_e2e = 1e3 * (time.perf_counter() - t0) / K
-    clocks = sampler.stop() if rank == 0 else None
+    e2e_err = float((host_out.to(dev) - case.out).abs().max())  # the two paths computed the same thing
     status = api.device_status()
-
     if world > 1:
-        t = torch.tensor([ms, ms_e2e] + ring_times, device=dev, dtype=torch.float64)
+        t = torch.tensor([ms_e2e, e2e_err], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
-        ring_times = [float(x) for x in t[2:]]
+        ms_e2e, e2e_err = float(t[0]), float(t[1])
+    checked = check_rows(api, torch, dist, w, rank, P, case.rows, case.dq, case.dk, case.dv, case.out, dev)
 
-    # causal-adjusted FLOPs; with documents the mask is block-diagonal causal (per document)
-    flops = causal_flops(B, H, S, D) if not doc_len else (S // doc_len) * causal_flops(B, H, doc_len, D)
-    peaks = measured_peaks()
-    checked = check_rows(api, torch, dist, w, rank, P, rows, dq, dk, dv, out, dev) if args.check_rows else None
-    schedule = None
-    launches_per_pass = P
-    if P > 1:
-        schedule = args.schedule if args.schedule != "auto" else (
-            "gather" if dk.numel() * dk.element_size() <= (32 << 20) else "ring")
-        if schedule == "gather":  # own shard, then the other P-1 shards 16 key segments per launch
-            per_launch = max(1, 16 // (w["n_splits"] if layout == 1 else 1))
-            launches_per_pass = 1 + -(-(P - 1) // per_launch)
     line = None
     if rank == 0:
-        value = flops / (ms * 1e-3) / 1e12
+        value = case.flops / (ms * 1e-3) / 1e12
         per_gpu = value / P
         h2d = sum(t.numel() * t.element_size() for t in host)
         d2h = host_out.numel() * host_out.element_size()
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": P, "steps": K,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
             "config": {"workload": w["name"], **{k: v for k, v in w.items() if k not in ("name", "seq_per_gpu")},
                        "cp_size": P, "per_gpu_tflops": per_gpu, "l2": "256 MB flush between timed iterations",
                        "timing": "CUDA events per pass on the launching stream, mean of K, max over ranks"},
-            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+            "e2e": {"value": case.flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "api": "ra_prefill_host" if P == 1 else "pinned H2D + ra_ring_prefill + D2H per rank"},
-            "gpu_launches": K * P * launches_per_pass,  # step kernels per pass on each of the P ranks
+                    "api": "ra_prefill_host" if P == 1 else "ra_ring_prefill_host",
+                    "max_abs_diff_vs_device_path": e2e_err},
+            # kernels of this library per pass on each rank (step kernels and the merge of partial states)
+            "gpu_launches": K * P * plan[2],
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": per_gpu / peaks["tflops"],
-                         # ncu, one launch of this workload at N = 1 (profiles/step_tc_kernel_config2_prefill.md)
-                         "traffic": 215.0e6 if (P == 1 and args.workload == "config2") else None,
-                         "traffic_unit": "bytes per launch (dram read + write, ncu)",
+                         "traffic": TRAFFIC_CONFIG2_N1 if (P == 1 and args.workload == "config2") else None,
+                         "traffic_unit": "bytes per launch (dram read + write; one ncu capture of this launch, "
+                                         "a constant of the workload, not re-measured by this run)",
                          "peak_source": f"{peaks['source']} bf16 GEMM burst",
                          "kernel": f"step_tc_kernel<{D}>"},
             "device_status": status,
-            "ring": {"total_ms": ring_times[0], "comp_ms": ring_times[1], "comm_ms": ring_times[2],
-                     "wait_ms": ring_times[3], "exposed_comm_frac": ring_times[3] / max(ring_times[0], 1e-9),
-                     "schedule": schedule, "step_launches_per_pass": launches_per_pass,
+            "ring": {"total_ms": times[1], "comp_ms": times[2], "comm_ms": times[3], "wait_ms": times[4],
+                     "exposed_comm_frac": times[4] / max(times[1], 1e-9),
+                     "schedule": plan[0] if P > 1 else None, "key_parts": plan[1],
+                     "kernel_launches_per_pass": plan[2],
                      "note": "one pass, max over ranks; wait = pass time not covered by step kernels"},
+            "checked_rows": checked,
         }
-        if checked is not None:
-            line["checked_rows"] = checked
-    if P > 1 and args.workload == "config2" and not args.no_decode:
-        dec = bench_ring_decode(api, torch, dist, dev, args, peaks, ring, rank, P)
+    del host, host_out
+    case.release()
+
+    # ---- decode (config 4) ----
+    if args.workload == "config2" and not args.no_decode:
+        dec = (bench_ring_decode(api, torch, dist, dev, args, peaks, ring, rank, P) if P > 1
+               else bench_decode(api, torch, dev, args, peaks))
         if rank == 0:
             line["decode"] = dec
-    if P == 1 and rank == 0 and args.workload == "config2":
-        if not args.no_decode:
-            line["decode"] = bench_decode(api, torch, dev, args, peaks)
-        if not args.no_cpu:
-            threads = min(host_threads(), 64)
-            dt, fl, desc, kind = cpu_reference_sample(threads)
-            line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
-                                    "sample": desc, "seconds": dt}
+
+    # ---- the other prefill workloads of the metric, as secondary objects of the same line ----
+    if args.workload == "config2" and not args.no_extra:
+        for name in ("config5", "config3"):
+            torch.cuda.empty_cache()
+            extra = Case(api, torch, name, P, rank, dev, want_host=False)
+            k2 = max(2, min(K, 5))
+            t2, c2 = time_case(api, torch, dist, extra, ring, args.schedule, k2, 2, world, dev, flush, sampler)
+            chk = check_rows(api, torch, dist, extra.w, rank, P, extra.rows, extra.dq, extra.dk, extra.dv,
+                             extra.out, dev)
+            rep = case_report(extra, t2, c2, peaks, plan_of(extra), chk)
+            rep["steps"], rep["warmup"] = k2, 2
+            if rank == 0:
+                line[name] = rep
+            extra.release()
+            del extra
+
+    if P == 1 and rank == 0 and args.workload == "config2" and not args.no_cpu:
+        threads = min(host_threads(), 64)
+        dt, fl, desc, kind = cpu_reference_sample(threads)
+        line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+                                "sample": desc, "seconds": dt}
     if rank == 0:
+        sampler.stop()
         print(json.dumps(line), flush=True)
     ring.close()
     if world > 1:
@@ -554,17 +632,60 @@ def bench_ring_decode(api, torch, dist, dev, args, peaks, ring, rank, P):
         ev[i][1].record(stream)
         t += 1
     torch.cuda.synchronize()
-    ms = torch.tensor([sum(a.elapsed_time(b) for a, b in ev) / n], device=dev, dtype=torch.float64)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms[0])
+    # one more step with the driver's own event timings: fold of the local shard / all-gather of the
+    # partials / whole step (the reference's RingResult fields, src/ring_decode.cu:206-224)
+    lens[t % P] += 1
+    rt = ring.decode_step(q, kn, vn, t % P, cache, lens, out, timed=True)
+    t += 1
+    tt = torch.tensor([sum(a.elapsed_time(b) for a, b in ev) / n, rt.comp_ms, rt.comm_ms, rt.total_ms],
+                      device=dev, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms, comp_ms, comm_ms, total_ms = (float(x) for x in tt)
+    checked = check_decode_rows(torch, dist, dev, cache, lens, q, out, rank, P)
     kv_bytes = 2.0 * B * kvH * L * D * 2
     gbs = kv_bytes / (ms * 1e-3) / 1e9
     return {"workload": f"decode B4 H32 kvH8 D128 fp16, 262144 cached tokens sharded over {P} ranks (config 4)",
             "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "hbm_gbs": gbs, "hbm_gbs_per_gpu": gbs / P,
+            "step": {"comp_ms": comp_ms, "comm_ms": comm_ms, "total_ms": total_ms,
+                     "note": "one step, max over ranks: split-K fold of the local shard, all-gather of the "
+                             "partials, whole step including the merge"},
+            "checked_rows": checked,
             "roofline": {"bound": "hbm", "achieved": gbs / P, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / P / peaks["hbm_gbs"], "traffic": None,
                          "peak_source": f"{peaks['source']} copy bandwidth",
                          "note": "per GPU, whole step including the all-gather of partials and the merge"}}
+
+
+def check_decode_rows(torch, dist, dev, cache, lens, q, out, rank, P):
+    """Parity of the sharded decode at full size: the output row of query head 0 of every batch
+    element against the CPU oracle over the cache rows of KV head 0 gathered from all ranks
+    (decode is unmasked: every cached row is visible). Untimed."""
+    import numpy as np
+
+    import oracle
+    kview, vview = cache.k_view(), cache.v_view()
+    n_max = max(lens)
+    worst = 0.0
+    B = q.shape[0]
+    for b in range(B):
+        kh = torch.zeros((n_max, q.shape[3]), dtype=kview.dtype, device=dev)
+        vh = torch.zeros_like(kh)
+        kh[:lens[rank]] = kview[b, 0, :lens[rank]]
+        vh[:lens[rank]] = vview[b, 0, :lens[rank]]
+        ks = [torch.empty_like(kh) for _ in range(P)]
+        vs = [torch.empty_like(vh) for _ in range(P)]
+        dist.all_gather(ks, kh)
+        dist.all_gather(vs, vh)
+        kg = torch.cat([ks[r][:lens[r]] for r in range(P)]).float().cpu().numpy()
+        vg = torch.cat([vs[r][:lens[r]] for r in range(P)]).float().cpu().numpy()
+        want, _ = oracle.attention_row(q[b, 0, 0].float().cpu().numpy(), kg, vg)
+        got = out[b, 0, 0].cpu().numpy()
+        err = np.abs(got - want)
+        assert np.all(err <= 1e-3 + 1e-3 * np.abs(want)), f"decode rank {rank} batch {b}: max err {err.max()}"
+        worst = max(worst, float(err.max()))
+    t = torch.tensor([worst], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"rows_per_rank": B, "max_abs_err": float(t[0]), "tolerance": "atol=rtol=1e-3 vs CPU oracle"}
 
 
 def main():
@@ -577,11 +698,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS),
                     help="prefill workload; config2 is the benchmark line, the others are for the tables")
-    ap.add_argument("--check-rows", action="store_true",
-                    help="also check a few output rows per rank against the CPU oracle (untimed)")
     ap.add_argument("--schedule", default="auto", choices=["auto", "ring", "gather"],
                     help="how K/V shards travel at N>1: hop-by-hop ring, one all-gather, or by shard size")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the secondary workloads (config 5 and config 3 objects of the line)")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.profile:
