@@ -102,8 +102,8 @@ RA_API int ra_attention_step(const float* q, const float* k, const float* v, flo
 
 /* One ring step, fp16 Q/K/V, fp32 state. Replaces launch_attention_step_fp16
  * (src/attention.hpp:147-150, src/attention_step_fp16.cu:256-326). Runs the tcgen05 kernel
- * for head_dim 32, 64 and 128 (32 on the 64-wide kernel, the loads zero-filling the upper half
- * of every row) and the SIMT kernel for 256. */
+ * for head_dim 32, 64, 128 and 256 (32 on the 64-wide kernel, the loads zero-filling the upper
+ * half of every row; 256 with one query tile per block). */
 RA_API int ra_attention_step_fp16(const void* q, const void* k, const void* v, float* out,
                                   float* m, float* l, const ra_shape* shape, int q_offset,
                                   int k_offset, int causal, ra_stream stream, int pos_stride);
@@ -134,6 +134,12 @@ RA_API int ra_attention_step_ex(int dtype, const void* q, const void* k, const v
                                 float* m, float* l, const ra_shape* shape, const ra_segmap* qmap,
                                 const ra_segmap* kmap, int pos_stride, unsigned flags,
                                 long long doc_len, int kv_row_stride, ra_stream stream);
+
+/* Which kernel the step entry points run for a dtype and head_dim (given 16-byte aligned
+ * tensors): 1 = the tcgen05 / TMA / tensor-memory kernel (fp16 and bf16, head_dim 32, 64, 128,
+ * 256), 0 = the SIMT fp32 kernel, -1 = unsupported. Host only. The reference dispatches on
+ * head_dim alone (src/attention_step_fp16.cu:275-292). */
+RA_API int ra_attention_step_path(int dtype, int head_dim);
 
 /* The general step over key segments that sit in n_shards stacked shards instead of one tensor:
  * k / v point at shard 0, every shard is (batch * kv_heads, shard_rows, head_dim) and shard s

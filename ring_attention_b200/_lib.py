@@ -142,6 +142,7 @@ _SIG = {
                                       C.POINTER(C.c_int), _P, _P, C.POINTER(RingResult)]),
     "ra_ring_decode_step_raw": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P,
                                           C.c_int, C.c_int, _P, _P, C.POINTER(RingResult)]),
+    "ra_attention_step_path": (C.c_int, [C.c_int, C.c_int]),
     "ra_debug_set_wait_limit_ns": (None, [C.c_ulonglong]),
     "ra_debug_stall_producer_after": (None, [C.c_int]),
 }

@@ -80,7 +80,8 @@ int step_ex(int dtype, const void* q, const void* k, const void* v, float* out, 
 }  // namespace
 
 bool step_stacked_supported(int dtype, int head_dim) {
-  return (dtype == RA_F16 || dtype == RA_BF16) && (head_dim == 32 || head_dim == 64 || head_dim == 128);
+  return (dtype == RA_F16 || dtype == RA_BF16) &&
+         (head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256);
 }
 
 int step_stacked(int dtype, const void* q, const void* k, const void* v, float* out, float* m,
@@ -90,7 +91,7 @@ int step_stacked(int dtype, const void* q, const void* k, const void* v, float* 
   RAB_REQUIRE(q && k && v && out && m && l && seg_shard && seg_row, RA_ERR_INVALID,
               "stacked step: null argument");
   RAB_REQUIRE(step_stacked_supported(dtype, s.head_dim), RA_ERR_INVALID,
-              "stacked step: needs a 16-bit dtype and head_dim 32, 64 or 128");
+              "stacked step: needs a 16-bit dtype and head_dim 32, 64, 128 or 256");
   RAB_REQUIRE(kmap.n_seg >= 1 && kmap.n_seg <= RA_MAX_SEG && kmap.seg_len >= 1 &&
                   kmap.n_seg * kmap.seg_len == s.seq_k && n_shards >= 1 && shard_rows >= 1,
               RA_ERR_INVALID, "stacked step: bad key map");
@@ -213,6 +214,11 @@ int ra_attention_step_stacked(int dtype, const void* q, const void* k, const voi
                       static_cast<cudaStream_t>(stream));
 }
 
+RA_API int ra_attention_step_path(int dtype, int head_dim) {
+  if (head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256) return -1;
+  if (dtype == RA_F16 || dtype == RA_BF16) return 1;
+  return dtype == RA_F32 ? 0 : -1;
+}
 RA_API void ra_debug_set_wait_limit_ns(unsigned long long ns) { rab::set_tc_wait_limit_ns(ns); }
 RA_API void ra_debug_stall_producer_after(int items) { rab::set_tc_stall_after(items); }
 

@@ -58,10 +58,8 @@ namespace rab {
 
 namespace {
 
-constexpr int kThreads = 384;
 constexpr int kBM = 128;           // query rows per tile (two tiles per block)
 constexpr int kBN = 128;           // keys per tile
-constexpr int kQBlock = 2 * kBM;   // query rows per block
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRowSumLimit = 32768.f;  // a tile's row sum of P above this moves the reference
@@ -351,23 +349,41 @@ __host__ __device__ constexpr unsigned make_idesc(unsigned fmt, unsigned b_mn, u
 
 template <int D, bool kPInTmem>
 struct TcCfg {
-  static constexpr int kTileBytes = kBM * D * 2;  // one 128-row tile of Q, K or V
-  static constexpr int kBoxes = D / 64;           // 64-element (128-byte) boxes per tile
-  static constexpr int kStages = kPInTmem ? (D == 128 ? 4 : 6) : (D == 128 ? 3 : 6);
+  // head_dim 256: O alone takes 256 tensor-memory columns, so a block owns ONE 128-row query
+  // tile (one MMA warp, one softmax group), and a 128-key K or V tile (64 KiB) travels through
+  // the ring as four 16 KiB items of 64 head_dim columns each, consumed one by one.
+  static constexpr int kTiles = D == 256 ? 1 : 2;            // query tiles per block
+  static constexpr int kThreads = 128 + 128 * kTiles;
+  static constexpr int kTileBytes = kBM * D * 2;             // one 128-row tile of Q, K or V
+  static constexpr int kBoxes = D / 64;                      // 64-element (128-byte) boxes per tile
+  static constexpr int kItemsPerTile = D == 256 ? 4 : 1;     // ring items per K / V tile
+  static constexpr int kBoxesPerItem = kBoxes / kItemsPerTile;
+  static constexpr int kItemBytes = kTileBytes / kItemsPerTile;
+  static constexpr int kStages = D == 256 ? (kPInTmem ? 10 : 8)
+                                          : (kPInTmem ? (D == 128 ? 4 : 6) : (D == 128 ? 3 : 6));
   static constexpr int kPBytes = kPInTmem ? 0 : kBM * kBN * 2;
   static constexpr int kOffQ = 0;
-  static constexpr int kOffKV = 2 * kTileBytes;
-  static constexpr int kOffP = kOffKV + kStages * kTileBytes;
-  static constexpr int kOffBar = kOffP + 2 * kPBytes;
+  static constexpr int kOffKV = kTiles * kTileBytes;
+  static constexpr int kOffP = kOffKV + kStages * kItemBytes;
+  static constexpr int kOffBar = kOffP + kTiles * kPBytes;
   static constexpr int kNumBars = 2 + 2 * kStages + 8;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + alignment slack
-  static constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
   // P does not overlap S when it lives in shared memory, or in tensor memory at head_dim 64
-  // (S 256 + O 128 + P 128 columns = 512). Then the next S tile can be issued as soon as the
-  // softmax threads hold the current one in registers, instead of after P is written.
-  static constexpr bool kEarlyS = !kPInTmem || D == 64;
-  static constexpr int kColP0 = (kPInTmem && D == 64) ? 384 : kColS0;
-  static constexpr int kColP1 = (kPInTmem && D == 64) ? 448 : kColS1;
+  // (S 256 + O 128 + P 128 columns = 512) and 256 (S 128 + O 256 + P 64 = 448). Then the next
+  // S tile can be issued as soon as the softmax threads hold the current one in registers,
+  // instead of after P is written.
+  static constexpr bool kEarlyS = !kPInTmem || D == 64 || D == 256;
+  static constexpr int kColS0 = 0, kColS1 = 128;
+  static constexpr int kColO0 = kTiles == 2 ? 256 : 128, kColO1 = 256 + D;
+  static constexpr int kColP0 = (kPInTmem && kEarlyS) ? 384 : kColS0;
+  static constexpr int kColP1 = (kPInTmem && kEarlyS) ? 448 : kColS1;
+  static constexpr int kPvN = D / kItemsPerTile;  // output columns one P.V instruction covers
+  // With one query tile per block 64 tensor-memory columns are left over: P is double-buffered
+  // (tile t in buffer t & 1, its completion on barrier o_done[t & 1]) so that the softmax of
+  // tile t+1 never waits for the long P.V of tile t.
+  static constexpr int kPBufs = (kTiles == 1 && kPInTmem) ? 2 : 1;
+  static_assert(kItemsPerTile == 1 || kEarlyS, "item-wise K/V needs the early-S schedule");
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 struct TileRange {
@@ -416,7 +432,7 @@ struct TcArgs {
 
 // DR is the head_dim of the tensors in memory: D, or 32 on the 64-wide kernel (see launch_cfg).
 template <int D, bool kBf16, bool kPInTmem, int DR>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((TcCfg<D, kPInTmem>::kThreads), 1)
     step_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const TcArgs a) {
@@ -461,7 +477,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int b = bh / a.H;
   const int kv_bh = b * a.kvH + (h % a.kvH);
   const int q_seg_len = a.qmap.seg_len;
-  const int row0 = tq * kQBlock;  // first row of the block inside its segment
+  constexpr int kQBlock = C::kTiles * kBM;  // query rows per block
+  const int row0 = tq * kQBlock;            // first row of the block inside its segment
   const int rows_in_block = min(kQBlock, q_seg_len - row0);
   const int qmin = a.qmap.base[sq] + row0 * a.stride;
   const int qmax = a.qmap.base[sq] + (row0 + rows_in_block - 1) * a.stride;
@@ -478,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(bar_q_full + 8, 1);
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_kv_full + 8 * s, 1);
-      mbar_init(bar_kv_empty + 8 * s, 2);  // one commit from each issuing warp
+      mbar_init(bar_kv_empty + 8 * s, C::kTiles);  // one commit from each issuing warp
     }
     for (int w = 0; w < 2; ++w) {
       mbar_init(bar_s_full + 8 * w, 1);
@@ -503,13 +520,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // Registers follow the work: the producer / MMA warpgroup gives most of its registers back,
   // the two softmax warpgroups (one row of 128 scores per thread) take them.
+  // (with one query tile per block there are 256 threads and registers to spare: no split)
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(RAB_REGS_LO));
+    if constexpr (C::kTiles == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(RAB_REGS_LO));
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ----
     if (lane == 0 && n_tiles > 0) {
       const int q_row = sq * q_seg_len + row0;
-      for (int w = 0; w < 2; ++w) {
+      for (int w = 0; w < C::kTiles; ++w) {
         mbar_expect_tx(bar_q_full + 8 * w, C::kTileBytes);
         for (int bx = 0; bx < C::kBoxes; ++bx)
           tma_load_3d(s_q + w * C::kTileBytes + bx * (kBM * 128), &tmap_q, bar_q_full + 8 * w,
@@ -522,7 +540,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int t = r.lo; t < r.hi && ok; ++t) {
           const int k_row = a.kseg_row[sk] + t * kBN;
           const int k_head = a.kseg_head[sk] + kv_bh;
-          for (int which = 0; which < 2 && ok; ++which, ++it) {
+          // ring items of this tile: K (all its items), then V; item = kBoxesPerItem boxes
+          for (int sub = 0; sub < 2 * C::kItemsPerTile && ok; ++sub, ++it) {
+            const int which = sub / C::kItemsPerTile;
+            const int box0 = (sub % C::kItemsPerTile) * C::kBoxesPerItem;
             const int slot = it % C::kStages;
             if (it >= C::kStages)
               ok = mbar_wait(bar_kv_empty + 8 * slot, ((it / C::kStages) + 1) & 1, abort_flag,
@@ -533,16 +554,16 @@ __global__ void __launch_bounds__(kThreads, 1)
               ok = false;
               break;
             }
-            mbar_expect_tx(bar_kv_full + 8 * slot, C::kTileBytes);
+            mbar_expect_tx(bar_kv_full + 8 * slot, C::kItemBytes);
             const CUtensorMap* map = which == 0 ? &tmap_k : &tmap_v;
-            for (int bx = 0; bx < C::kBoxes; ++bx)
-              tma_load_3d(s_kv + slot * C::kTileBytes + bx * (kBN * 128), map,
-                          bar_kv_full + 8 * slot, bx * 64, k_row, k_head);
+            for (int bx = 0; bx < C::kBoxesPerItem; ++bx)
+              tma_load_3d(s_kv + slot * C::kItemBytes + bx * (kBN * 128), map,
+                          bar_kv_full + 8 * slot, (box0 + bx) * 64, k_row, k_head);
           }
         }
       }
     }
-  } else if (warp == 1 || warp == 2) {
+  } else if (warp == 1 || (warp == 2 && C::kTiles == 2)) {
     // ------------------------------------------------------------- MMA issuers ----
     // One issuing warp per query tile (warp 1: tile 0, warp 2: tile 1). The two tiles are
     // independent instruction streams, so a tile that is still in its exponentials never holds
@@ -555,7 +576,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int w = warp - 1;
       constexpr unsigned kFmt = kBf16 ? 1u : 0u;
       constexpr unsigned idesc_s = make_idesc(kFmt, 0, kBN, kBM);
-      constexpr unsigned idesc_pv = make_idesc(kFmt, 1, D, kBM);
+      constexpr unsigned idesc_pv = make_idesc(kFmt, 1, C::kPvN, kBM);
       const unsigned t_s = tmem_base + (w == 0 ? C::kColS0 : C::kColS1);
       const unsigned t_o = tmem_base + (w == 0 ? C::kColO0 : C::kColO1);
       [[maybe_unused]] const unsigned t_p = tmem_base + (w == 0 ? C::kColP0 : C::kColP1);
@@ -563,43 +584,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       [[maybe_unused]] const unsigned long long pd = desc_kmajor(s_p + w * C::kPBytes);
       const unsigned long long dkv0_k = desc_kmajor(s_kv);
       const unsigned long long dkv0_v = desc_mnmajor(s_kv, kBN * 128, 1024);
-      constexpr unsigned kSlotUnits = C::kTileBytes >> 4;  // one ring slot in 16-byte units
+      constexpr unsigned kItemUnits = C::kItemBytes >> 4;  // one ring slot in 16-byte units
+      constexpr unsigned kBox = (kBM * 128) >> 4;          // one 64-element box in 16-byte units
+      constexpr int kIPT = C::kItemsPerTile;
       const unsigned b_s_full = bar_s_full + 8 * w, b_s_free = bar_s_free + 8 * w;
       const unsigned b_p_full = bar_p_full + 8 * w, b_o_done = bar_o_done + 8 * w;
-      // S_w = Q_w K^T, then `then_bar` (and the slot's release) from the same elected lane
-      auto issue_s = [&](int slot) {
-        const unsigned long long kd = dkv0_k + static_cast<unsigned long long>(slot * kSlotUnits);
-        if (elect_one()) {
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            constexpr unsigned kBox = (kBM * 128) >> 4;
-            const unsigned off = (ks / 4) * kBox + (ks % 4) * 2;  // 64-element box, 32 B per step
-            mma_ss(t_s, qd + off, kd + off, idesc_s, ks > 0 ? 1u : 0u);
-          }
-        }
-      };
-      auto issue_pv = [&](int slot, bool acc) {
-        const unsigned long long vd = dkv0_v + static_cast<unsigned long long>(slot * kSlotUnits);
-        if (elect_one()) {
-#pragma unroll
-          for (int ks = 0; ks < kBN / 16; ++ks) {
-            const unsigned long long bd = vd + ks * (2048 >> 4);  // 16 keys = two 8-row groups
-            const unsigned accum = (acc || ks > 0) ? 1u : 0u;
-            if constexpr (kPInTmem) {
-              mma_ts(t_o, t_p + ks * 8, bd, idesc_pv, accum);
-            } else {
-              constexpr unsigned kBox = (kBM * 128) >> 4;
-              mma_ss(t_o, pd + ((ks / 4) * kBox + (ks % 4) * 2), bd, idesc_pv, accum);
-            }
-          }
-        }
-      };
-      auto commit2 = [&](unsigned bar_a, unsigned bar_b) {
-        if (elect_one()) {
-          tc_commit(bar_a);
-          tc_commit(bar_b);
-        }
-      };
       auto wait = [&](unsigned bar, unsigned parity, int which, int tile) {
         return __all_sync(0xffffffffu,
                           mbar_wait(bar, parity, abort_flag, a.status, which, tile, a.wait_ns)) != 0;
@@ -607,53 +596,104 @@ __global__ void __launch_bounds__(kThreads, 1)
       auto wait_kv = [&](int it, int which, int tile) {
         return wait(bar_kv_full + 8 * (it % C::kStages), (it / C::kStages) & 1, which, tile);
       };
-      // K_t is ring item 2t, V_t is item 2t+1
-      bool ok = wait_kv(0, 2, 0) && wait(bar_q_full + 8 * w, 0, 3, w);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-        commit2(b_s_full, bar_kv_empty);
-      }
+      // Ring items of key tile t: K items [2t * kIPT, ...), V items [(2t + 1) * kIPT, ...).
+      // The k-steps of one K item of S_w = Q_w K^T (called by the elected lane).
+      auto s_ksteps = [&](int slot, int sub) {
+        const unsigned long long kd = dkv0_k + static_cast<unsigned long long>(slot * kItemUnits);
+#pragma unroll
+        for (int ks = 0; ks < C::kBoxesPerItem * 4; ++ks) {
+          // 64-element box, 32 B per k-step; Q holds all boxes, the item only its own
+          const unsigned off_q = (sub * C::kBoxesPerItem + ks / 4) * kBox + (ks % 4) * 2;
+          const unsigned off_k = (ks / 4) * kBox + (ks % 4) * 2;
+          mma_ss(t_s, qd + off_q, kd + off_k, idesc_s, (sub > 0 || ks > 0) ? 1u : 0u);
+        }
+      };
+      // The k-steps of one V item of O_w += P_w V: kPvN output columns.
+      auto pv_ksteps = [&](int slot, int sub, bool acc, [[maybe_unused]] int pbuf) {
+        const unsigned long long vd = dkv0_v + static_cast<unsigned long long>(slot * kItemUnits);
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          const unsigned long long bd = vd + ks * (2048 >> 4);  // 16 keys = two 8-row groups
+          const unsigned accum = (acc || ks > 0) ? 1u : 0u;
+          if constexpr (kPInTmem) {
+            mma_ts(t_o + sub * C::kPvN, t_p + pbuf * 64 + ks * 8, bd, idesc_pv, accum);
+          } else {
+            mma_ss(t_o + sub * C::kPvN, pd + ((ks / 4) * kBox + (ks % 4) * 2), bd, idesc_pv, accum);
+          }
+        }
+      };
+      // S_w(t): every K item as it lands; an item's slot is released by a commit behind its last
+      // k-step, the softmax group is signalled behind the last item.
+      auto do_s = [&](int t) {
+        bool good = true;
+#pragma unroll
+        for (int sub = 0; sub < kIPT && good; ++sub) {
+          const int it = 2 * t * kIPT + sub, slot = it % C::kStages;
+          good = wait_kv(it, 5, t);
+          if (!good) break;
+          tc_fence_after();
+          if (elect_one()) {
+            s_ksteps(slot, sub);
+            if (sub == kIPT - 1) tc_commit(b_s_full);
+            tc_commit(bar_kv_empty + 8 * slot);
+          }
+        }
+        return good;
+      };
+      // O_w += P_w V_t, one V item at a time.
+      auto do_pv = [&](int t) {
+        bool good = true;
+#pragma unroll
+        for (int sub = 0; sub < kIPT && good; ++sub) {
+          const int it = (2 * t + 1) * kIPT + sub, slot = it % C::kStages;
+          good = wait_kv(it, 4, t);
+          if (!good) break;
+          tc_fence_after();
+          if (elect_one()) {
+            const int pbuf = C::kPBufs == 2 ? (t & 1) : 0;
+            pv_ksteps(slot, sub, t > 0, pbuf);
+            if (sub == kIPT - 1) tc_commit(b_o_done + 8 * pbuf);
+            tc_commit(bar_kv_empty + 8 * slot);
+          }
+        }
+        return good;
+      };
+      bool ok = wait(bar_q_full + 8 * w, 0, 3, w) && do_s(0);
       for (int t = 0; t < n_tiles && ok; ++t) {
-        const int it_v = 2 * t + 1, it_k = 2 * t + 2;
-        const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
         const bool more = t + 1 < n_tiles;
         if constexpr (C::kEarlyS) {
           // S_w(t+1) goes out as soon as the softmax threads hold S_w(t) in registers; P.V of
           // tile t follows when its P is written. The tensor core works on the next scores
           // while the exponentials of the current tile run.
-          if (more) {
-            ok = wait_kv(it_k, 5, t) && wait(b_s_free, t & 1, 9, t);
-            if (!ok) break;
-            tc_fence_after();
-            issue_s(slot_k);
-            commit2(b_s_full, bar_kv_empty + 8 * slot_k);
-          }
-          ok = wait_kv(it_v, 4, t) && wait(b_p_full, t & 1, 6, t);
-          if (!ok) break;
-          tc_fence_after();
-          issue_pv(slot_v, t > 0);
-          commit2(b_o_done, bar_kv_empty + 8 * slot_v);
+          if (more) ok = wait(b_s_free, t & 1, 9, t) && do_s(t + 1);
+          ok = ok && wait(b_p_full, t & 1, 6, t) && do_pv(t);
         } else {
-          // P aliases S: P.V of tile t and the scores of tile t+1 go out together once P_w(t)
-          // is written (the scores' completion tells the softmax group that P.V is done too).
+          // P aliases S (whole tiles are single ring items here): P.V of tile t and the scores
+          // of tile t+1 go out in one batch once P_w(t) is written; the scores' completion
+          // tells the softmax group that P.V is done as well.
+          const int it_v = 2 * t + 1, it_k = 2 * t + 2;
+          const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
           ok = wait_kv(it_v, 4, t) && (!more || wait_kv(it_k, 5, t)) && wait(b_p_full, t & 1, 6, t);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(slot_v, t > 0);
-          if (more) {
-            issue_s(slot_k);
-            commit2(b_s_full, bar_kv_empty + 8 * slot_v);
-            if (elect_one()) tc_commit(bar_kv_empty + 8 * slot_k);
-          } else {
-            commit2(b_o_done, bar_kv_empty + 8 * slot_v);
+          if (elect_one()) {
+            pv_ksteps(slot_v, 0, t > 0, 0);
+            if (more) {
+              s_ksteps(slot_k, 0);
+              tc_commit(b_s_full);
+              tc_commit(bar_kv_empty + 8 * slot_v);
+              tc_commit(bar_kv_empty + 8 * slot_k);
+            } else {
+              tc_commit(b_o_done);
+              tc_commit(bar_kv_empty + 8 * slot_v);
+            }
           }
         }
       }
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(RAB_REGS_HI));
+    if constexpr (C::kTiles == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(RAB_REGS_HI));
     // ----------------------------------------------------------------- softmax ----
     const int w = (warp - 4) >> 2;                   // query tile of this warpgroup
     const int row = ((warp & 3) << 5) + lane;        // row inside the tile = TMEM lane
@@ -752,7 +792,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           if constexpr (kPInTmem) {
             // keys 64h .. 64h+63 as 32 packed columns (over the consumed S columns when P aliases S)
-            tmem_st32u(t_p + h * 32, &pk[0]);
+            tmem_st32u(t_p + (C::kPBufs == 2 ? (j & 1) * 64 : 0) + h * 32, &pk[0]);
           } else {
             // K-major 128B-swizzled P tile: row r, 16-byte piece q of 64-key box h at
             // h * 16 KiB + r * 128 + ((q ^ (r & 7)) * 16)
@@ -767,11 +807,20 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         };
-        // P_w(j-1) must have been consumed (and O_w must be at rest) before P_w(j) is written or
-        // O_w rescaled: wait for PV_w(j-1), issued a whole softmax ago. (With P aliased over S
-        // the completed S_w(j) already implies it.)
-        auto wait_prev_pv = [&]() {
-          if constexpr (C::kEarlyS) {
+        // The P buffer about to be written must have been consumed: wait for PV_w(j-1), issued a
+        // whole softmax ago (PV_w(j-2) with two P buffers). With P aliased over S the completed
+        // S_w(j) already implies it. `all` also waits for PV_w(j-1) when P is double-buffered: O_w
+        // must be at rest before it is rescaled.
+        auto wait_prev_pv = [&](bool all) {
+          if constexpr (C::kPBufs == 2) {
+            for (int back = all ? 1 : 2; back <= 2 && ok; ++back) {
+              const int t = j - back;
+              if (t < 0) continue;
+              ok = mbar_wait(bar_o_done + 8 * (t & 1), (t >> 1) & 1, abort_flag, a.status, 10, j, a.wait_ns);
+              ok = __all_sync(0xffffffffu, ok);
+            }
+            if (ok) tc_fence_after();
+          } else if constexpr (C::kEarlyS) {
             if (j > 0) {
               ok = mbar_wait(bar_o_done + 8 * w, (j - 1) & 1, abort_flag, a.status, 10, j, a.wait_ns);
               ok = __all_sync(0xffffffffu, ok);
@@ -786,7 +835,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
           sum_a = make_float2(0.f, 0.f);
           sum_b = make_float2(0.f, 0.f);
-          wait_prev_pv();
+          wait_prev_pv(false);
           if (!ok) break;
           half_tile(0, neg_m);
           half_tile(1, neg_m);
@@ -794,10 +843,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           slow = __any_sync(0xffffffffu, !(row_sum <= kRowSumLimit)) != 0;  // also catches NaN
         }
         else {
-          wait_prev_pv();
+          wait_prev_pv(true);
           if (!ok) break;
         }
         if (slow) {
+          if constexpr (C::kPBufs == 2) {  // O must be at rest: also PV_w(j-1)
+            wait_prev_pv(true);
+            if (!ok) break;
+          }
           float m0 = s[0], m1 = s[1], m2 = s[2], m3 = s[3];  // four independent chains
 #pragma unroll
           for (int i = 4; i < kBN; i += 8) {
@@ -851,8 +904,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ---------------------------------------------------------------- epilogue ----
     if (ok && n_tiles > 0)
-      ok = mbar_wait(bar_o_done + 8 * w, C::kEarlyS ? ((n_tiles - 1) & 1) : 0, abort_flag, a.status,
-                     8, n_tiles, a.wait_ns);
+      ok = C::kPBufs == 2
+               ? mbar_wait(bar_o_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag,
+                           a.status, 8, n_tiles, a.wait_ns)
+               : mbar_wait(bar_o_done + 8 * w, C::kEarlyS ? ((n_tiles - 1) & 1) : 0, abort_flag,
+                           a.status, 8, n_tiles, a.wait_ns);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
@@ -988,6 +1044,7 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.H = a.H;
   t.kvH = a.kvH;
   t.Sq = a.Sq;
+  constexpr int kQBlock = C::kTiles * kBM;
   t.n_qblocks_per_seg = (a.qmap.seg_len + kQBlock - 1) / kQBlock;
   t.qmap = a.qmap;
   t.kmap = a.kmap;
@@ -1007,7 +1064,7 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   auto kern = step_tc_kernel<D, kBf16, kPInTmem, DR>;
   RAB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   const dim3 grid(static_cast<unsigned>(a.B) * a.H, static_cast<unsigned>(n_qblocks));
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, t);
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, t);
   RAB_CUDA(cudaGetLastError());
   return RA_OK;
 }
@@ -1037,7 +1094,7 @@ int launch_d(int dtype, const StepArgs& a, cudaStream_t stream) {
 
 bool step_tc_supported(int dtype, const StepArgs& a) {
   if (dtype != RA_F16 && dtype != RA_BF16) return false;
-  if (a.D != 32 && a.D != 64 && a.D != 128) return false;
+  if (a.D != 32 && a.D != 64 && a.D != 128 && a.D != 256) return false;
   if (a.Sq <= 0 || a.Sk <= 0) return false;
   if (a.qmap.n_seg * a.qmap.seg_len != a.Sq || a.kmap.n_seg * a.kmap.seg_len != a.Sk) return false;
   if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
@@ -1051,7 +1108,8 @@ int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream) {
   // head_dim 32 runs on the 64-wide kernel: the loads zero-fill the upper half of every row
   // (see make_map), so the scores are exact and the upper 32 output columns are never stored
   if (a.D == 32 || a.D == 64) return launch_d<64>(dtype, a, stream);
-  return launch_d<128>(dtype, a, stream);
+  if (a.D == 128) return launch_d<128>(dtype, a, stream);
+  return launch_d<256>(dtype, a, stream);
 }
 
 

@@ -199,9 +199,32 @@ def test_ragged_shapes_fp16(shape, causal):
     assert_close(got, want, 1e-3, 1e-3, "out")
 
 
+def test_every_reference_head_dim_takes_the_tensor_core_kernel_in_16_bit():
+    from ring_attention_b200._lib import RA_BF16, RA_F16, RA_F32, lib
+    for D in (32, 64, 128, 256):  # reference src/attention_step_fp16.cu:275-292
+        assert lib().ra_attention_step_path(RA_F16, D) == 1
+        assert lib().ra_attention_step_path(RA_BF16, D) == 1
+        assert lib().ra_attention_step_path(RA_F32, D) == 0
+    assert lib().ra_attention_step_path(RA_F16, 48) == -1
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_dim_256_long_rows_both_kernels_agree_with_the_oracle(dtype):
+    # several key tiles per row, GQA, ragged lengths, end-aligned causal mask: the tcgen05 kernel
+    # (one query tile per block, K / V tiles through the ring as four items) and the SIMT kernel
+    q, k, v = normal_inputs(77, 1, 4, 2, 300, 1100, 256, scale=0.7)
+    q, k, v = (round_to(x, dtype) for x in (q, k, v))
+    want = oracle.cpu_attention(q, k, v, True, kv_heads=2)
+    qmap, kmap = SegMap.make([1100 - 300], 300), SegMap.make([0], 1100)
+    tol = 1e-3 if dtype == torch.float16 else 8e-3
+    for kwargs in ({}, {"p_in_smem": True}, {"force_simt": True}):
+        got, _ = run_ex(q, k, v, qmap, kmap, 1, True, dtype, 2, **kwargs)
+        assert_close(got, want, tol, tol, f"D=256 {dtype} {kwargs}")
+
+
 @pytest.mark.parametrize("p_in_smem", [False, True])
 def test_both_p_paths_of_the_tensor_core_kernel(p_in_smem):
-    for D in (32, 64, 128):
+    for D in (32, 64, 128, 256):
         q, k, v = normal_inputs(30 + D, 1, 2, 2, 384, 1664, D)
         q, k, v = (round_to(x, torch.float16) for x in (q, k, v))
         want = oracle.cpu_attention(q, k, v, True, kv_heads=2)
@@ -374,14 +397,14 @@ def test_stacked_shards_fold_several_ring_steps_in_one_launch(dtype, D, layout, 
 
 
 def test_stacked_step_rejects_what_the_tensor_core_kernel_cannot_read():
-    q = torch.zeros((1, 1, 64, 256), device="cuda", dtype=torch.float16)
-    ks = torch.zeros((2, 1, 1, 64, 256), device="cuda", dtype=torch.float16)
-    out, m, l = state(1, 1, 64, 256)
+    q = torch.zeros((1, 1, 64, 64), device="cuda", dtype=torch.float32)
+    ks = torch.zeros((2, 1, 1, 64, 64), device="cuda", dtype=torch.float32)
+    out, m, l = state(1, 1, 64, 64)
     qm, km = SegMap(), SegMap()
     qm.n_seg, qm.seg_len = 1, 64
     km.n_seg, km.seg_len = 2, 64
-    with pytest.raises(RuntimeError):  # head_dim 256 has no tensor-core kernel
-        api.attention_step_stacked(q, ks, ks, out, m, l, api.AttentionShape(1, 1, 64, 128, 256, 1), qm, km,
+    with pytest.raises(RuntimeError):  # fp32 has no tensor-core kernel
+        api.attention_step_stacked(q, ks, ks, out, m, l, api.AttentionShape(1, 1, 64, 128, 64, 1), qm, km,
                                    [0, 1], [0, 0])
     q64 = torch.zeros((1, 1, 64, 64), device="cuda", dtype=torch.float16)
     ks64 = torch.zeros((2, 1, 1, 64, 64), device="cuda", dtype=torch.float16)
