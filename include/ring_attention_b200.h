@@ -330,6 +330,7 @@ typedef struct ra_ring_config {
   int n_splits;  /* zig-zag sub-groups per rank (2 * zigzag_n) */
   long long doc_len; /* 0 = no document mask */
   int schedule;      /* RA_SCHEDULE_*; 0 (auto) picks by shard size */
+  int ring2d_nodes;  /* RA_SCHEDULE_RING2D: number of rank groups N (cp_size = N * G); else unused */
 } ra_ring_config;
 
 /* How the K/V shards reach every rank. RING is the reference's overlapped hop-by-hop rotation
@@ -338,7 +339,20 @@ typedef struct ra_ring_config {
  * RingMode::AllGather does, src/ring_loop.cu:273-420, but still one masked step per source
  * shard). AUTO takes GATHER while a shard tensor is at most 32 MiB, where a hop's latency
  * cannot hide under a step, and RING above. Results are identical. */
-enum { RA_SCHEDULE_AUTO = 0, RA_SCHEDULE_RING = 1, RA_SCHEDULE_GATHER = 2 };
+enum {
+  RA_SCHEDULE_AUTO = 0,
+  RA_SCHEDULE_RING = 1,
+  RA_SCHEDULE_GATHER = 2,
+  /* RingMode::RingBlocking (src/ring_loop.cu:259-592): the rotation with nothing overlapped,
+   * every exchange on the compute stream behind its step. The baseline the overlap is measured
+   * against. */
+  RA_SCHEDULE_BLOCKING = 3,
+  /* RingMode::Ring2D (src/ring_loop.cu:1071-1550) in the visitation order of Ring2DSchedule
+   * (src/ring2d_schedule.cpp:28-42): ring2d_nodes groups of ranks; the outer exchange of a
+   * macro-step runs on the side stream under the inner ring's steps. On one NVSwitch box all
+   * links are alike, so this is for comparison and for parity with the reference's CLI. */
+  RA_SCHEDULE_RING2D = 4
+};
 
 /* Mirrors RingResult (src/ring_loop.hpp:30-36); times of this rank, milliseconds. */
 typedef struct ra_ring_result {

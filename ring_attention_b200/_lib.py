@@ -47,7 +47,7 @@ class RingConfig(C.Structure):
     _fields_ = [("batch", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("seq", C.c_int),
                 ("head_dim", C.c_int), ("dtype", C.c_int), ("causal", C.c_int),
                 ("layout", C.c_int), ("n_splits", C.c_int), ("doc_len", C.c_longlong),
-                ("schedule", C.c_int)]
+                ("schedule", C.c_int), ("ring2d_nodes", C.c_int)]
 
 
 class RingResult(C.Structure):

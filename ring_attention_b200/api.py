@@ -375,14 +375,15 @@ class Ring:
             pass
 
     def prefill(self, q, k, v, *, seq, causal, layout=0, n_splits=2, doc_len=0, want_lse=False,
-                timed=False, out=None, schedule="auto"):
+                timed=False, out=None, schedule="auto", ring2d_nodes=1):
         """One overlapped ring pass (``run_ring_attention`` in ring-overlap mode, reference
         src/ring_loop_fp16.cu:522-818) over this rank's device shards. ``schedule`` is "ring"
-        (hop-by-hop rotation), "gather" (one all-gather, the reference's allgather mode) or
-        "auto" (by shard size)."""
+        (hop-by-hop rotation, overlapped), "gather" (one all-gather, the reference's allgather mode),
+        "blocking" (the rotation with nothing overlapped, ring-blocking), "ring2d" (ring-2d over
+        ``ring2d_nodes`` groups of ranks) or "auto" (gather or ring by shard size)."""
         B, H, sloc, D = q.shape
-        cfg = RingConfig(B, H, k.shape[1], seq, D, _dtype(q), int(causal), layout, n_splits,
-                         doc_len, {"auto": 0, "ring": 1, "gather": 2}[schedule])
+        cfg = self._cfg(B, H, k.shape[1], seq, D, _dtype(q), causal, layout, n_splits, doc_len, schedule,
+                        ring2d_nodes)
         need = lib().ra_ring_prefill_workspace_bytes(self._h, C.byref(cfg))
         if self._work is None or self._work.numel() < need:
             self._work = torch.empty(need, dtype=torch.uint8, device=q.device)
@@ -400,19 +401,22 @@ class Ring:
             ret.append(res)
         return ret[0] if len(ret) == 1 else tuple(ret)
 
-    def _cfg(self, B, H, kvH, seq, D, dtype, causal, layout, n_splits, doc_len, schedule):
+    SCHEDULES = {"auto": 0, "ring": 1, "gather": 2, "blocking": 3, "ring2d": 4}
+
+    def _cfg(self, B, H, kvH, seq, D, dtype, causal, layout, n_splits, doc_len, schedule, nodes=1):
         return RingConfig(B, H, kvH, seq, D, dtype, int(causal), layout, n_splits, doc_len,
-                          {"auto": 0, "ring": 1, "gather": 2}[schedule])
+                          self.SCHEDULES[schedule], nodes)
 
     def plan(self, *, batch, heads, kv_heads, seq, head_dim, dtype=torch.float16, causal=True, layout=0,
-             n_splits=2, doc_len=0, schedule="auto"):
+             n_splits=2, doc_len=0, schedule="auto", ring2d_nodes=1):
         """(schedule name, key parts, kernel launches per pass) of ``prefill`` for this config."""
         cfg = self._cfg(batch, heads, kv_heads, seq, head_dim, _DT[dtype], causal, layout, n_splits,
-                        doc_len, schedule)
+                        doc_len, schedule, ring2d_nodes)
         sched, parts, launches = C.c_int(), C.c_int(), C.c_int()
         check(lib().ra_ring_prefill_plan(self._h, C.byref(cfg), C.byref(sched), C.byref(parts),
                                          C.byref(launches)))
-        return {1: "ring", 2: "gather"}[sched.value], parts.value, launches.value
+        names = {v: k for k, v in self.SCHEDULES.items()}
+        return names[sched.value], parts.value, launches.value
 
     def prefill_host(self, q, k, v, out, *, seq, causal, layout=0, n_splits=2, doc_len=0, lse=None,
                      schedule="auto", timed=False):

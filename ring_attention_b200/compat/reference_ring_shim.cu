@@ -163,7 +163,21 @@ RingResult run_ring_attention(const RingConfig& cfg) {
   rc.layout = lay.mode;
   rc.n_splits = lay.n_splits;
   rc.doc_len = 0;
-  rc.schedule = cfg.mode == RingMode::AllGather ? RA_SCHEDULE_GATHER : RA_SCHEDULE_AUTO;
+  // every --mode runs the schedule it names (AUTO, which picks by shard size, is for the library
+  // API). ring-2d groups ranks by node as the reference does (src/ring_loop.cu:1079-1091): one
+  // node here, unless RA_RING2D_NODES asks for more groups to exercise the two-tier order.
+  rc.ring2d_nodes = 1;
+  switch (cfg.mode) {
+    case RingMode::AllGather: rc.schedule = RA_SCHEDULE_GATHER; break;
+    case RingMode::RingBlocking: rc.schedule = RA_SCHEDULE_BLOCKING; break;
+    case RingMode::Ring2D: {
+      rc.schedule = RA_SCHEDULE_RING2D;
+      const char* e = std::getenv("RA_RING2D_NODES");
+      const int nodes = e ? std::atoi(e) : 1;
+      if (nodes >= 1 && cfg.cp_size % nodes == 0) rc.ring2d_nodes = nodes;
+    } break;
+    default: rc.schedule = RA_SCHEDULE_RING; break;
+  }
   const size_t work_bytes = ra_ring_prefill_workspace_bytes(ring, &rc);
   DeviceTensor<signed char> work(work_bytes);
 

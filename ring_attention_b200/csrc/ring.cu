@@ -274,6 +274,11 @@ static int check_cfg(const ra_ring* r, const ra_ring_config* c) {
     RAB_REQUIRE(c->seq % (c->n_splits * r->cp) == 0, RA_ERR_INVALID,
                 "seq=%d must be divisible by n_splits*cp_size=%d", c->seq, c->n_splits * r->cp);
   }
+  RAB_REQUIRE(c->schedule >= RA_SCHEDULE_AUTO && c->schedule <= RA_SCHEDULE_RING2D, RA_ERR_INVALID,
+              "ring prefill: unknown schedule %d", c->schedule);
+  if (c->schedule == RA_SCHEDULE_RING2D)
+    RAB_REQUIRE(c->ring2d_nodes >= 1 && r->cp % c->ring2d_nodes == 0, RA_ERR_INVALID,
+                "ring-2d: cp_size=%d must be a multiple of ring2d_nodes=%d", r->cp, c->ring2d_nodes);
   return RA_OK;
 }
 
@@ -288,7 +293,9 @@ constexpr size_t kGatherMaxBytes = static_cast<size_t>(32) << 20;
 
 static bool use_gather(const ra_ring* r, const ra_ring_config* c, size_t kv_raw) {
   if (r->cp <= 1) return false;
-  if (c->schedule == RA_SCHEDULE_RING) return false;
+  if (c->schedule == RA_SCHEDULE_RING || c->schedule == RA_SCHEDULE_BLOCKING ||
+      c->schedule == RA_SCHEDULE_RING2D)
+    return false;
   if (c->schedule == RA_SCHEDULE_GATHER) return true;
   return kv_raw <= kGatherMaxBytes;
 }
@@ -345,7 +352,8 @@ size_t ra_ring_prefill_workspace_bytes(const ra_ring* r, const ra_ring_config* c
     const GatherPlan g = gather_plan(r, c);
     if (g.parts >= 2) kv += align256((g.parts + 1) * g.part_floats * sizeof(float));
   } else if (r->cp > 1) {
-    kv = 4 * kv_bytes;
+    // ring: two K/V pairs (double buffer); 2-D ring: two for the inner and two for the outer ring
+    kv = (c->schedule == RA_SCHEDULE_RING2D ? 8 : 4) * kv_bytes;
   }
   return kv + 2 * ml + 256;
 }
@@ -358,7 +366,10 @@ int ra_ring_prefill_plan(const ra_ring* r, const ra_ring_config* c, int* schedul
   const size_t es = c->dtype == RA_F32 ? 4 : 2;
   const size_t kv_raw =
       static_cast<size_t>(c->batch) * kvH * (c->seq / r->cp) * c->head_dim * es;
-  int sched = RA_SCHEDULE_RING, parts = 1, n = r->cp;
+  int sched = (c->schedule == RA_SCHEDULE_BLOCKING || c->schedule == RA_SCHEDULE_RING2D)
+                  ? c->schedule
+                  : RA_SCHEDULE_RING;
+  int parts = 1, n = r->cp;
   if (use_gather(r, c, kv_raw)) {
     sched = RA_SCHEDULE_GATHER;
     const GatherPlan g = gather_plan(r, c);
@@ -400,6 +411,8 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
   const bool gather = use_gather(r, c, kv_raw);
   unsigned char* buf_k[2] = {nullptr, nullptr};
   unsigned char* buf_v[2] = {nullptr, nullptr};
+  unsigned char* outer_k[2] = {nullptr, nullptr};  // 2-D ring: receive buffers of the outer ring
+  unsigned char* outer_v[2] = {nullptr, nullptr};
   GatherPlan plan{};
   float* part_base = nullptr;
   if (P > 1 && gather) {
@@ -417,6 +430,13 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
     buf_k[1] = base + 2 * kv_bytes;
     buf_v[1] = base + 3 * kv_bytes;
     base += 4 * kv_bytes;
+    if (c->schedule == RA_SCHEDULE_RING2D) {
+      for (int i = 0; i < 2; ++i) {
+        outer_k[i] = base + (2 * i) * kv_bytes;
+        outer_v[i] = base + (2 * i + 1) * kv_bytes;
+      }
+      base += 4 * kv_bytes;
+    }
   }
   float* m = reinterpret_cast<float*>(base);
   float* l = reinterpret_cast<float*>(base + align256(rows * sizeof(float)));
@@ -438,6 +458,7 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
   }
   if (q_ready) RAB_CUDA(cudaStreamWaitEvent(stream, q_ready, 0));
   int n_launch = 0;  // timed compute intervals of this pass
+  int n_comm = gather ? 1 : P - 1;  // timed transfer intervals
   if (gather) {
     const bool split = plan.parts >= 2;
     auto part_out = [&](int p) { return part_base + static_cast<size_t>(p) * plan.part_floats; };
@@ -515,11 +536,93 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
     RAB_CUDA(cudaEventRecord(r->ev_comp[1], stream));
     n_launch = 2;
   }
-  for (int s = 0; s < P && !gather; ++s) {
+  // RA_SCHEDULE_BLOCKING (the reference's ring-blocking, src/ring_loop.cu:259-592): the same
+  // rotation with nothing overlapped. The exchange of a step is enqueued on the compute stream
+  // behind the step kernel, so every step is transfer, then compute.
+  const bool blocking = c->schedule == RA_SCHEDULE_BLOCKING;
+  const bool ring2d = c->schedule == RA_SCHEDULE_RING2D && P > 1;
+  auto exchange = [&](cudaStream_t cs, const void* src_k, const void* src_v, void* dst_k, void* dst_v,
+                      int to, int from) {
+    NcclGroup grp;
+    grp.note(g_nccl.Send(src_k, kv_raw, kNcclInt8, to, r->comm, cs), "ncclSend(K)");
+    grp.note(g_nccl.Recv(dst_k, kv_raw, kNcclInt8, from, r->comm, cs), "ncclRecv(K)");
+    grp.note(g_nccl.Send(src_v, kv_raw, kNcclInt8, to, r->comm, cs), "ncclSend(V)");
+    grp.note(g_nccl.Recv(dst_v, kv_raw, kNcclInt8, from, r->comm, cs), "ncclRecv(V)");
+    return grp.end();
+  };
+  // RA_SCHEDULE_RING2D (the reference's ring-2d, src/ring_loop.cu:1071-1550, visitation order of
+  // Ring2DSchedule, src/ring2d_schedule.cpp:28-42): the ranks form `ring2d_nodes` groups of
+  // G = cp / nodes. In macro-step m a rank first sends the shard it starts the macro-step with
+  // (its "seed") to the same slot of the next group on the side stream, which overlaps the whole
+  // inner loop; the inner loop computes against the seed and rotates it around the group's own
+  // ring G - 1 times on the compute stream (as the reference does); the shard received from the
+  // previous group is the next seed.
+  auto ring2d_pass = [&]() -> int {
+    const int N = c->ring2d_nodes, G = P / N;
+    const int n = r->rank / G, g = r->rank % G;
+    const int intra_next = n * G + (g + 1) % G, intra_prev = n * G + (g - 1 + G) % G;
+    const int outer_next = ((n + 1) % N) * G + g, outer_prev = ((n - 1 + N) % N) * G + g;
+    const void* seed_k = k;
+    const void* seed_v = v;
+    int idx = 0;
+    n_comm = N - 1;
+    for (int mstep = 0; mstep < N; ++mstep) {
+      NvtxRange range("ring prefill: 2-D macro-step");
+      if (mstep < N - 1) {
+        // the buffer received into was the seed of the macro-step before the last one: everything
+        // enqueued on the compute stream so far has to be through with it
+        RAB_CUDA(cudaEventRecord(r->ev_aux[0], stream));
+        RAB_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_aux[0], 0));
+        RAB_CUDA(cudaEventRecord(r->ev_comm_begin[mstep], r->comm_stream));
+        int rc2 = exchange(r->comm_stream, seed_k, seed_v, outer_k[mstep & 1], outer_v[mstep & 1],
+                           outer_next, outer_prev);
+        if (rc2 != RA_OK) {
+          cudaStreamSynchronize(r->comm_stream);
+          return rc2;
+        }
+        RAB_CUDA(cudaEventRecord(r->ev_comm[mstep], r->comm_stream));
+      }
+      const void* cur_k = seed_k;
+      const void* cur_v = seed_v;
+      for (int i = 0; i < G; ++i, ++idx) {
+        const int src = ((n - mstep + N) % N) * G + (g - i + G) % G;
+        const int step = (r->rank - src + P) % P;
+        ra_segmap qmap, kmap;
+        const int stride =
+            ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, step, &qmap, &kmap);
+        RAB_REQUIRE(stride >= 1, RA_ERR_INVALID, "ring prefill: bad partition");
+        unsigned flags = c->causal ? RA_STEP_CAUSAL : 0u;
+        if (idx == 0) flags |= RA_STEP_FRESH;
+        if (idx == P - 1) flags |= RA_STEP_FINALIZE;
+        if (idx == 0 && q_ready) RAB_CUDA(cudaStreamWaitEvent(stream, q_ready, 0));
+        RAB_CUDA(cudaEventRecord(r->ev_comp_begin[idx], stream));
+        int rc2 = ra_attention_step_ex(c->dtype, q, cur_k, cur_v, out, m, l, &shape, &qmap, &kmap,
+                                       stride, flags, c->doc_len, 0, stream);
+        if (rc2 == RA_OK && i < G - 1) {
+          rc2 = exchange(stream, cur_k, cur_v, buf_k[i & 1], buf_v[i & 1], intra_next, intra_prev);
+          cur_k = buf_k[i & 1];
+          cur_v = buf_v[i & 1];
+        }
+        if (rc2 != RA_OK) {
+          cudaStreamSynchronize(r->comm_stream);
+          return rc2;
+        }
+        RAB_CUDA(cudaEventRecord(r->ev_comp[idx], stream));
+      }
+      if (mstep < N - 1) {
+        RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[mstep], 0));
+        seed_k = outer_k[mstep & 1];
+        seed_v = outer_v[mstep & 1];
+      }
+    }
+    n_launch = P;
+    return RA_OK;
+  };
+  for (int s = 0; s < P && !gather && !ring2d; ++s) {
     NvtxRange range("ring prefill: step");
     const void* cur_k = s == 0 ? k : buf_k[(s - 1) & 1];
     const void* cur_v = s == 0 ? v : buf_v[(s - 1) & 1];
-    if (s < P - 1) {
+    if (s < P - 1 && !blocking) {
       // the buffer about to be received into was the source of compute step s-1
       if (s >= 1) RAB_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_comp[s - 1], 0));
       RAB_CUDA(cudaEventRecord(r->ev_comm_begin[s], r->comm_stream));
@@ -536,7 +639,7 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
       RAB_CUDA(cudaEventRecord(r->ev_comm[s], r->comm_stream));
     }
     if (s == 0 && q_ready) RAB_CUDA(cudaStreamWaitEvent(stream, q_ready, 0));
-    if (s > 0) RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[s - 1], 0));
+    if (s > 0 && !blocking) RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[s - 1], 0));
     ra_segmap qmap, kmap;
     const int stride =
         ra_ring_step_maps(P, r->rank, c->seq, c->layout, c->n_splits, s, &qmap, &kmap);
@@ -553,6 +656,16 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
     }
     RAB_CUDA(cudaEventRecord(r->ev_comp[s], stream));
     n_launch = s + 1;
+    if (s < P - 1 && blocking) {
+      RAB_CUDA(cudaEventRecord(r->ev_comm_begin[s], stream));
+      rc = exchange(stream, cur_k, cur_v, buf_k[s & 1], buf_v[s & 1], next, prev);
+      if (rc != RA_OK) return rc;
+      RAB_CUDA(cudaEventRecord(r->ev_comm[s], stream));
+    }
+  }
+  if (ring2d) {
+    rc = ring2d_pass();
+    if (rc != RA_OK) return rc;
   }
   if (lse) {
     rc = ra_attention_lse(m, l, lse, rows, stream);
@@ -572,7 +685,7 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
       RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_comp_begin[s], r->ev_comp[s]));
       comp += ms;
     }
-    for (int s = 0; s < (gather ? 1 : P - 1); ++s) {
+    for (int s = 0; s < n_comm; ++s) {
       RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_comm_begin[s], r->ev_comm[s]));
       comm += ms;
     }

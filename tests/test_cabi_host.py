@@ -152,3 +152,28 @@ def test_ring2d_schedule_bit_exact_and_covering(N, G):
             assert seen[0] == n * G + g
     for bad in [(0, 2, 0, 0, 0, 0), (2, 2, 2, 0, 0, 0), (2, 2, 0, 2, 0, 0), (2, 2, 0, 0, 2, 0), (2, 2, 0, 0, 0, -1)]:
         assert L.ra_ring2d_source(*bad) == -1
+
+
+@pytest.mark.parametrize("N,G", [(1, 4), (2, 2), (2, 4), (4, 2), (8, 1)])
+def test_ring2d_data_movement_delivers_the_shard_the_schedule_names(N, G):
+    """The 2-D ring driver moves shards like this: per macro-step the seed goes to the same slot of
+    the next group, and inside the group the current shard rotates G - 1 times. Played on shard
+    ids, every rank must hold exactly Ring2DSchedule::source(m, i) at (m, i) (reference
+    src/ring2d_schedule.cpp:28-42) and see every shard once."""
+    L = lib()
+    P = N * G
+    seed = list(range(P))  # shard id every rank starts the macro-step with
+    seen = [[] for _ in range(P)]
+    for m in range(N):
+        cur = list(seed)
+        for i in range(G):
+            for r in range(P):
+                n, g = divmod(r, G)
+                assert cur[r] == L.ra_ring2d_source(N, G, n, g, m, i)
+                seen[r].append(cur[r])
+            if i < G - 1:  # inner ring: g -> g + 1 inside the group
+                cur = [cur[(r // G) * G + (r % G - 1) % G] for r in range(P)]
+        # outer ring: the seed of this macro-step arrives from the same slot of the previous group
+        seed = [seed[((r // G - 1) % N) * G + r % G] for r in range(P)]
+    for r in range(P):
+        assert sorted(seen[r]) == list(range(P))

@@ -39,7 +39,8 @@ def _worker(rank, world, port, case, ret):
                 out, lse, res = ring.prefill(ql, kl, vl, seq=S, causal=case["causal"], layout=case["layout"],
                                              n_splits=case["n_splits"], doc_len=case.get("doc_len", 0),
                                              want_lse=True, timed=True,
-                                             schedule=case.get("schedule", "auto"))
+                                             schedule=case.get("schedule", "auto"),
+                                             ring2d_nodes=case.get("nodes", 1))
             torch.cuda.synchronize()
             assert api.device_status()[0] == 0
             qf, kf, vf = (t.float().numpy() for t in (q, k, v))
@@ -98,8 +99,20 @@ def _run(world, case):
     procs = [ctx.Process(target=_worker, args=(r, world, port, case, ret)) for r in range(world)]
     for p in procs:
         p.start()
+    try:
+        for p in procs:
+            p.join(300)
+    finally:
+        # a rank still running here is stuck: end exactly the processes started above, so that no
+        # rank keeps its communicator and GPU after the test
+        stuck = [p for p in procs if p.is_alive()]
+        for p in stuck:
+            p.terminate()
+        for p in stuck:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
     for p in procs:
-        p.join(300)
         assert p.exitcode == 0, f"rank exited with {p.exitcode}"
     assert len(ret) == world
     for r in range(world):
@@ -139,6 +152,18 @@ def test_ring_prefill_fp32_and_bf16(schedule):
                      schedule=schedule, dtype="f32"))
     _run(world, dict(kind="prefill", B=1, H=2, kvH=2, S=world * 2 * 160, D=128, causal=True, layout=2, n_splits=2,
                      schedule=schedule, dtype="bf16"))
+
+
+@pytest.mark.parametrize("layout,n_splits", [(1, 2), (2, 2)])
+def test_ring_blocking_and_2d_schedules(layout, n_splits):
+    # the reference's ring-blocking and ring-2d modes (src/ring_loop.cu:259-592, 1071-1550) as
+    # schedules over the same kernels: results as for the overlapped ring
+    world = _world()
+    base = dict(kind="prefill", B=1, H=4, kvH=2, S=world * n_splits * 256, D=64, causal=True, layout=layout,
+                n_splits=n_splits)
+    _run(world, dict(base, schedule="blocking"))
+    for nodes in sorted({1, 2, world}):  # one group, two groups, every rank its own group
+        _run(world, dict(base, schedule="ring2d", nodes=nodes))
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16"])

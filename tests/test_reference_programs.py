@@ -4,6 +4,7 @@ reftests; binaries under oracle/_ref/tests). Each program carries its own oracle
 cpu_attention) and tolerances (1e-4 fp32, 1e-2 fp16, 1e-3 / 5e-2 decode, exact cache equality)
 and returns 0 on success."""
 import os
+import signal
 import subprocess
 
 import pytest
@@ -52,10 +53,22 @@ def mpirun(n, prog, *args, timeout=600):
     if not (os.path.exists(launcher) and os.path.exists(path)):
         pytest.skip(f"{prog} was not built (oracle/_ref/tests is made where the reference tree is mounted)")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MINIMPI_TIMEOUT_S="120")
-    r = subprocess.run([launcher, "-n", str(n), path, *args], capture_output=True, text=True, timeout=timeout,
-                       env=env)
-    assert r.returncode == 0, f"{prog} {args} failed:\n{r.stdout[-2000:]}\n{r.stderr[-2000:]}"
-    return r.stdout
+    # the launcher and its ranks get a process group of their own, so that a timeout can end all of
+    # them (and only them) instead of leaving ranks behind with their communicators and GPUs
+    proc = subprocess.Popen([launcher, "-n", str(n), path, *args], stdout=subprocess.PIPE,
+                            stderr=subprocess.PIPE, text=True, env=env, start_new_session=True)
+    try:
+        out, err = proc.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGTERM)
+        try:
+            out, err = proc.communicate(timeout=10)
+        except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)
+            out, err = proc.communicate()
+        raise AssertionError(f"{prog} {args} timed out after {timeout} s:\n{out[-2000:]}\n{err[-2000:]}")
+    assert proc.returncode == 0, f"{prog} {args} failed:\n{out[-2000:]}\n{err[-2000:]}"
+    return out
 
 
 SMOKE = ["--seq", "128", "--heads", "2", "--head_dim", "32", "--iters", "1", "--causal", "1"]

@@ -6,8 +6,11 @@ memory to its own arena, or the call sits in a section that must not enter the C
 library. This file checks, through the C ABI, that it returns what the ordinary entry point
 returns (same tolerances as the other decode tests: 1e-5 for fp32, 1e-3 for fp16), on two calls
 in a row (the array is shared and keeps the previous call's contents), and that a problem too
-large for the array is refused with a message that names the limit. It is collected last on
-purpose and must also pass alone in a fresh process.
+large for the array is refused with a message that names the limit. A third case is sized so
+that the array forces fewer key splits than the scheduler would like (the branch that makes this
+entry point different), and is checked against the CPU oracle directly; around a warmed-up call
+the free device memory must not move. It is collected last on purpose and must also pass alone
+in a fresh process.
 """
 import ctypes as C
 
@@ -15,6 +18,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from ring_attention_b200 import api
 from ring_attention_b200._lib import RA_F16, RA_F32, lib
 from util import assert_close
@@ -59,6 +63,51 @@ def test_noalloc_decode_matches_the_ordinary_entry_point_twice_in_a_row(dtype, c
         assert_close(got, want, tol, tol, f"out B{B} H{H} L{L}")
         assert_close(got_m, want_m, tol, tol, "m")
         assert np.isfinite(got).all()
+
+
+def test_noalloc_decode_with_the_split_count_capped_by_the_array_against_the_oracle():
+    # batch 8 x 64 heads x (128 + 2) floats per split leaves room for 3 splits in the 262144-float
+    # array, far fewer than the ~14 the scheduler wants on 148 SMs: the capped branch runs
+    B, H, kvH, D, L = 8, 64, 8, 128, 3000
+    assert 262144 // (B * H * (D + 2)) == 3
+    g = torch.Generator(device="cuda").manual_seed(99)
+    k = torch.randn((B, kvH, L, D), generator=g, device="cuda").to(torch.float16)
+    v = torch.randn((B, kvH, L, D), generator=g, device="cuda").to(torch.float16)
+    q = torch.randn((B, H, 1, D), generator=g, device="cuda").to(torch.float16)
+    shape = api.AttentionShape(B, H, 1, L, D, kvH)
+    got, _ = call("noalloc", RA_F16, q, k, v, shape, False, 0, L)  # warms up: address lookup, attributes
+    free_before = torch.cuda.mem_get_info()[0]
+    got, _ = call("noalloc", RA_F16, q, k, v, shape, False, 0, L)
+    assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
+    want = oracle.cpu_attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(),
+                                False, kv_heads=kvH)
+    assert_close(got, want, 1e-3, 1e-3, "capped splits vs CPU oracle")
+    plain, _ = call("plain", RA_F16, q, k, v, shape, False, 0, L)
+    assert_close(got, plain, 1e-3, 1e-3, "capped splits vs ordinary entry point")
+
+
+def test_noalloc_decode_on_a_second_device_if_there_is_one():
+    # the array's address is looked up per device: a call on device 1 must use device 1's copy
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with torch.cuda.device(1):
+        g = torch.Generator(device="cuda:1").manual_seed(5)
+        B, H, kvH, D, L = 2, 8, 2, 64, 2000
+        k = torch.randn((B, kvH, L, D), generator=g, device="cuda:1").to(torch.float16)
+        v = torch.randn((B, kvH, L, D), generator=g, device="cuda:1").to(torch.float16)
+        q = torch.randn((B, H, 1, D), generator=g, device="cuda:1").to(torch.float16)
+        shape = api.AttentionShape(B, H, 1, L, D, kvH)
+        out = torch.zeros((B, H, 1, D), device="cuda:1")
+        m = torch.full((B, H, 1), -float("inf"), device="cuda:1")
+        l = torch.zeros((B, H, 1), device="cuda:1")
+        api.check(lib().ra_attention_decode_step_noalloc(
+            RA_F16, api._ptr(q), api._ptr(k), api._ptr(v), api._ptr(out), api._ptr(m), api._ptr(l),
+            C.byref(shape.c()), 0, 0, 0, api._stream(), L))
+        api.launch_attention_finalize(out, l, shape)
+        torch.cuda.synchronize()
+        want = oracle.cpu_attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(),
+                                    False, kv_heads=kvH)
+        assert_close(out.cpu().numpy(), want, 1e-3, 1e-3, "device 1 vs CPU oracle")
 
 
 def test_noalloc_decode_refuses_problems_beyond_its_scratch():
