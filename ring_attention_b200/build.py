@@ -35,7 +35,7 @@ def _stale(target, deps):
 
 def _compile(src, verbose):
     obj = os.path.join(OBJ, src[:-3] + ".o")
-    deps = [os.path.join(CSRC, src), os.path.join(CSRC, "common.cuh"),
+    deps = [os.path.join(CSRC, src), os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tc_common.cuh"),
             os.path.join(HERE, "..", "include", "ring_attention_b200.h")]
     if not _stale(obj, deps):
         return obj, ""
@@ -46,6 +46,28 @@ def _compile(src, verbose):
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
     return obj, r.stderr
+
+
+PROBE_SRC = os.path.join(CSRC, "probe")
+PROBE_BIN = os.path.join(PROBE_SRC, "_bin")
+
+
+def build_probes() -> list:
+    """The stand-alone timing probes under csrc/probe (measurement tools behind the design notes;
+    nothing in the library links them) into csrc/probe/_bin/<name>."""
+    os.makedirs(PROBE_BIN, exist_ok=True)
+    outs = []
+    for f in sorted(os.listdir(PROBE_SRC)):
+        if not f.endswith(".cu"):
+            continue
+        src, exe = os.path.join(PROBE_SRC, f), os.path.join(PROBE_BIN, f[:-3])
+        if _stale(exe, [src]):
+            r = subprocess.run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
+                                "-std=c++17", "-o", exe, src], capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"nvcc failed on {f}:\n{r.stdout}\n{r.stderr}")
+        outs.append(exe)
+    return outs
 
 
 def build(verbose: bool = False, force: bool = False) -> str:
@@ -72,3 +94,5 @@ def build(verbose: bool = False, force: bool = False) -> str:
 
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    if "--probes" in sys.argv:
+        print("\n".join(build_probes()))

@@ -328,8 +328,11 @@ static GatherPlan gather_plan(const ra_ring* r, const ra_ring_config* c) {
     const int need = (g.entries + RA_MAX_SEG - 1) / RA_MAX_SEG;
     const long long blocks =
         static_cast<long long>(c->batch) * c->heads * g.nsg * ((seg_len + 255) / 256);
-    long long want = blocks > 0 ? (2ll * r->sm_count + blocks - 1) / blocks : 1;
-    if (want > 4) want = 4;
+    // Measured on one GPU playing a rank of 8 (config 2: 128 query blocks, 14 entries): one part
+    // 180-331 us depending on the rank, two parts 184-188, three 195-230, four 190-195, seven
+    // 225 (more launches, each with its own prologue and partial state to merge). So: split in
+    // two as soon as the query blocks alone leave SMs idle, and no further.
+    long long want = blocks > 0 && blocks < 2ll * r->sm_count ? 2 : 1;
     g.parts = need > want ? need : static_cast<int>(want);
     if (g.parts > g.entries) g.parts = g.entries > 0 ? g.entries : 1;
     if (g.parts > kMaxKeyParts) g.stacked = false;
