@@ -74,6 +74,8 @@ int step_ex(int dtype, const void* q, const void* k, const void* v, float* out, 
   }
   if (!(flags & RA_STEP_FORCE_SIMT) && step_tc_supported(dtype, a))
     return launch_step_tc(dtype, a, stream);
+  if (!(flags & RA_STEP_FORCE_SIMT) && step_tf32_supported(dtype, a))
+    return launch_step_tf32(a, stream);
   return launch_step_simt(dtype, a, stream);
 }
 
@@ -217,7 +219,8 @@ int ra_attention_step_stacked(int dtype, const void* q, const void* k, const voi
 RA_API int ra_attention_step_path(int dtype, int head_dim) {
   if (head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256) return -1;
   if (dtype == RA_F16 || dtype == RA_BF16) return 1;
-  return dtype == RA_F32 ? 0 : -1;
+  if (dtype == RA_F32) return (head_dim == 32 || head_dim == 64) ? 2 : 0;
+  return -1;
 }
 RA_API void ra_debug_set_wait_limit_ns(unsigned long long ns) { rab::set_tc_wait_limit_ns(ns); }
 RA_API void ra_debug_stall_producer_after(int items) { rab::set_tc_stall_after(items); }

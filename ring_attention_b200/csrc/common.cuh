@@ -113,6 +113,9 @@ struct StepArgs {
 int launch_step_simt(int dtype, const StepArgs& a, cudaStream_t stream);
 int launch_step_tc(int dtype, const StepArgs& a, cudaStream_t stream);
 bool step_tc_supported(int dtype, const StepArgs& a);
+// fp32 on the tensor cores through split TF32 operands (step_tf32.cu): head_dim 32 and 64
+int launch_step_tf32(const StepArgs& a, cudaStream_t stream);
+bool step_tf32_supported(int dtype, const StepArgs& a);
 
 // One step over key segments that live in several stacked shards (see StepArgs::kseg_head):
 // k / v point at shard 0, every shard is (B * kvH, shard_rows, D) and shard s starts

@@ -276,6 +276,16 @@ __device__ inline unsigned long long desc_mnmajor(unsigned saddr, unsigned lbo_b
   return (static_cast<unsigned long long>(hi) << 32) | lo;
 }
 
+// MN-major operand of 32-bit elements (TF32): the 128B swizzle that moves 32-byte pieces (TMA's
+// SWIZZLE_128B_ATOM_32B), four rows of the contraction index per swizzle atom. Leading byte
+// offset = distance between 32-element N blocks, stride = between 4-row groups (512 B).
+__device__ inline unsigned long long desc_mnmajor_32b(unsigned saddr, unsigned lbo_bytes,
+                                                      unsigned sbo_bytes) {
+  const unsigned lo = ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+  const unsigned hi = ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (1u << 29);
+  return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+
 // Instruction descriptor, kind::f16: fp32 accumulate, A/B format (0 fp16, 1 bf16), A K-major,
 // B K-major (b_mn = 0) or MN-major (1), N >> 3 at bit 17, M >> 4 at bit 24.
 __host__ __device__ constexpr unsigned make_idesc(unsigned fmt, unsigned b_mn, unsigned n,
@@ -355,7 +365,8 @@ inline EncodeTiledFn encode_fn() {
 // the tensor (head_dim 32 in 16 bits) the upper elements of every row are out of bounds and
 // arrive as zeros, which is exactly a head_dim 64 tile whose upper half is zero.
 inline int make_map(CUtensorMap* map, int dtype, const void* base, int D, long long rows,
-                    long long heads, long long head_stride_elems, int box_rows = 128) {
+                    long long heads, long long head_stride_elems, int box_rows = 128,
+                    bool swizzle_32b_atoms = false) {
   EncodeTiledFn fn = encode_fn();
   RAB_REQUIRE(fn != nullptr, RA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
   const cuuint64_t es = dtype == RA_F32 ? 4 : 2;
@@ -369,7 +380,8 @@ inline int make_map(CUtensorMap* map, int dtype, const void* base, int D, long l
                                    : dtype == RA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult r = fn(map, type, 3, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle_32b_atoms ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RAB_REQUIRE(r == CUDA_SUCCESS, RA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d",
               static_cast<int>(r));

@@ -94,6 +94,22 @@ def test_fp32_step_reference_case_list(case):
     assert_close(lse, want_lse, 1e-5, 1e-5, "lse")
 
 
+@pytest.mark.parametrize("D", [32, 64])
+def test_fp32_tensor_core_and_simt_kernels_agree_with_the_oracle_at_1e5(D):
+    # long rows, GQA, ragged lengths, end-aligned causal mask, inputs of mixed magnitudes: the
+    # split-TF32 kernel (hi*hi + lo*hi + hi*lo) must hold the fp32 tolerance like the SIMT one
+    q, k, v = normal_inputs(5 + D, 1, 4, 2, 333, 1500, D)
+    q[:, :, :, 0] *= 2.0
+    k[:, :, ::7] *= 0.05
+    v[:, :, ::5] *= 3.0
+    want, want_lse = oracle.cpu_attention(q, k, v, True, kv_heads=2, want_lse=True)
+    qmap, kmap = SegMap.make([1500 - 333], 333), SegMap.make([0], 1500)
+    for force_simt in (False, True):
+        got, lse = run_ex(q, k, v, qmap, kmap, 1, True, torch.float32, 2, force_simt=force_simt)
+        assert_close(got, want, 1e-5, 1e-5, f"out D={D} simt={force_simt}")
+        assert_close(lse, want_lse, 1e-5, 1e-5, f"lse D={D} simt={force_simt}")
+
+
 def test_config1_fp32_noncausal_mha_output_and_lse():
     # B1 H8 S1024 D64 fp32 N(0,1), non-causal, one rank: output and log-sum-exp element-wise
     q, k, v = normal_inputs(42, 1, 8, 8, 1024, 1024, 64)
@@ -204,7 +220,8 @@ def test_every_reference_head_dim_takes_the_tensor_core_kernel_in_16_bit():
     for D in (32, 64, 128, 256):  # reference src/attention_step_fp16.cu:275-292
         assert lib().ra_attention_step_path(RA_F16, D) == 1
         assert lib().ra_attention_step_path(RA_BF16, D) == 1
-        assert lib().ra_attention_step_path(RA_F32, D) == 0
+        # fp32: split-TF32 tensor-core kernel for head_dim 32 / 64, SIMT above
+        assert lib().ra_attention_step_path(RA_F32, D) == (2 if D <= 64 else 0)
     assert lib().ra_attention_step_path(RA_F16, 48) == -1
 
 
