@@ -311,6 +311,7 @@ struct GatherPlan {
   int nsg;             // key segments per shard
   int entries;         // (cp - 1) * nsg
   int parts;           // launches over the entries
+  int chunks;          // head groups gathered (and folded) one after the other
   size_t part_floats;  // floats of one partial state [O | m | l]
 };
 
@@ -338,6 +339,11 @@ static GatherPlan gather_plan(const ra_ring* r, const ra_ring_config* c) {
     if (g.parts > kMaxKeyParts) g.stacked = false;
   }
   if (!g.stacked) g.parts = 1;
+  // With one batch row and one KV head per query head the heads are independent, contiguous
+  // slices of every tensor: the gather then travels as two halves of the heads, and the fold of
+  // the first half runs while the second half is still on the wire.
+  const int kvH = c->kv_heads > 0 ? c->kv_heads : c->heads;
+  g.chunks = (g.stacked && c->batch == 1 && kvH == c->heads && kvH % 2 == 0 && r->cp >= 2) ? 2 : 1;
   return g;
 }
 
@@ -378,7 +384,7 @@ int ra_ring_prefill_plan(const ra_ring* r, const ra_ring_config* c, int* schedul
     const GatherPlan g = gather_plan(r, c);
     if (g.stacked) {
       parts = g.parts;
-      n = 1 + g.parts + (g.parts >= 2 ? 1 : 0);  // own shard, the parts, the merge
+      n = 1 + g.chunks * g.parts + (g.parts >= 2 ? 1 : 0);  // own shard, the parts, the merge
     }
   }
   if (schedule) *schedule = sched;
@@ -451,12 +457,27 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
   RAB_CUDA(cudaStreamWaitEvent(r->comm_stream, r->ev_start, 0));
   if (gather) {
     NvtxRange range("ring prefill: all-gather K/V");
+    // chunk g = heads [g * kvH / chunks, ...): a contiguous slice of the rank's K and V; the
+    // gathered chunk is (P, kvH / chunks, sloc, D), chunks one after the other in the buffer
+    const size_t chunk_raw = kv_raw / plan.chunks;
     RAB_CUDA(cudaEventRecord(r->ev_comm_begin[0], r->comm_stream));
-    NcclGroup grp;
-    grp.note(g_nccl.AllGather(k, buf_k[0], kv_raw, kNcclInt8, r->comm, r->comm_stream), "ncclAllGather(K)");
-    grp.note(g_nccl.AllGather(v, buf_v[0], kv_raw, kNcclInt8, r->comm, r->comm_stream), "ncclAllGather(V)");
-    rc = grp.end();
-    if (rc != RA_OK) return rc;
+    for (int g = 0; g < plan.chunks; ++g) {
+      NcclGroup grp;
+      grp.note(g_nccl.AllGather(static_cast<const unsigned char*>(k) + g * chunk_raw,
+                                buf_k[0] + static_cast<size_t>(g) * P * chunk_raw, chunk_raw, kNcclInt8,
+                                r->comm, r->comm_stream),
+               "ncclAllGather(K)");
+      grp.note(g_nccl.AllGather(static_cast<const unsigned char*>(v) + g * chunk_raw,
+                                buf_v[0] + static_cast<size_t>(g) * P * chunk_raw, chunk_raw, kNcclInt8,
+                                r->comm, r->comm_stream),
+               "ncclAllGather(V)");
+      rc = grp.end();
+      if (rc != RA_OK) {
+        cudaStreamSynchronize(r->comm_stream);
+        return rc;
+      }
+      if (plan.chunks > 1) RAB_CUDA(cudaEventRecord(r->ev_comm[1 + g], r->comm_stream));
+    }
     RAB_CUDA(cudaEventRecord(r->ev_comm[0], r->comm_stream));
   }
   if (q_ready) RAB_CUDA(cudaStreamWaitEvent(stream, q_ready, 0));
@@ -479,7 +500,7 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
                               causal_flag | RA_STEP_FRESH, c->doc_len, 0, stream);
     if (rc != RA_OK) return rc;
     RAB_CUDA(cudaEventRecord(r->ev_comp[0], stream));
-    RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[0], 0));
+    if (plan.chunks == 1) RAB_CUDA(cudaStreamWaitEvent(stream, r->ev_comm[0], 0));
     RAB_CUDA(cudaEventRecord(r->ev_comp_begin[1], stream));
     if (!plan.stacked) {
       // one plain step per shard, in ring order
@@ -498,32 +519,45 @@ static int ring_prefill_impl(ra_ring* r, const ra_ring_config* c, const void* q,
       // entry e = (s - 1) * nsg + i: sub-group i of the shard s hops away; part z takes the
       // entries e = z, z + parts, ... so every part sees keys from all over the sequence
       bool aux_used[kAuxStreams] = {false, false, false};
-      for (int z = 0; z < plan.parts; ++z) {
-        ra_segmap ks;
-        int seg_shard[RA_MAX_SEG], seg_row[RA_MAX_SEG];
-        stride = ra_ring_gather_part_maps(P, r->rank, c->seq, c->layout, c->n_splits, plan.parts, z,
-                                          &ks, seg_shard, seg_row);
-        RAB_REQUIRE(stride >= 1 && ks.n_seg >= 1 && ks.seg_len == kmap.seg_len, RA_ERR_INVALID,
-                    "ring prefill: bad partition");
-        const PosMap km = make_posmap(ks);
-        ra_shape sh = shape;
-        sh.seq_k = km.n_seg * km.seg_len;
-        cudaStream_t st = stream;
-        if (z > 0) {
-          const int a = (z - 1) % kAuxStreams;
-          st = r->aux_stream[a];
-          if (!aux_used[a]) {
-            RAB_CUDA(cudaStreamWaitEvent(st, r->ev_start, 0));
-            RAB_CUDA(cudaStreamWaitEvent(st, r->ev_comm[0], 0));
-            aux_used[a] = true;
+      const int heads_c = c->heads / plan.chunks;  // query (= KV) heads per chunk
+      const size_t chunk_raw = kv_raw / plan.chunks;
+      for (int g = 0; g < plan.chunks; ++g) {
+        cudaEvent_t landed = plan.chunks > 1 ? r->ev_comm[1 + g] : r->ev_comm[0];
+        if (plan.chunks > 1) RAB_CUDA(cudaStreamWaitEvent(stream, landed, 0));
+        const size_t q_off = static_cast<size_t>(g) * heads_c * sloc * c->head_dim;  // elements
+        const size_t r_off = static_cast<size_t>(g) * heads_c * sloc;               // rows
+        const unsigned char* gk = buf_k[0] + static_cast<size_t>(g) * P * chunk_raw;
+        const unsigned char* gv = buf_v[0] + static_cast<size_t>(g) * P * chunk_raw;
+        for (int z = 0; z < plan.parts; ++z) {
+          ra_segmap ks;
+          int seg_shard[RA_MAX_SEG], seg_row[RA_MAX_SEG];
+          stride = ra_ring_gather_part_maps(P, r->rank, c->seq, c->layout, c->n_splits, plan.parts, z,
+                                            &ks, seg_shard, seg_row);
+          RAB_REQUIRE(stride >= 1 && ks.n_seg >= 1 && ks.seg_len == kmap.seg_len, RA_ERR_INVALID,
+                      "ring prefill: bad partition");
+          const PosMap km = make_posmap(ks);
+          ra_shape sh = shape;
+          sh.seq_k = km.n_seg * km.seg_len;
+          if (plan.chunks > 1) sh.heads = sh.kv_heads = heads_c;
+          cudaStream_t st = stream;
+          if (z > 0) {
+            const int a = (z - 1) % kAuxStreams;
+            st = r->aux_stream[a];
+            if (!aux_used[a]) {
+              RAB_CUDA(cudaStreamWaitEvent(st, r->ev_start, 0));
+              aux_used[a] = true;
+            }
+            RAB_CUDA(cudaStreamWaitEvent(st, landed, 0));
           }
+          const unsigned flags = split ? (causal_flag | RA_STEP_FRESH) : (causal_flag | RA_STEP_FINALIZE);
+          float* o_z = (split ? part_out(z + 1) : out) + q_off;
+          float* m_z = (split ? part_m(z + 1) : m) + r_off;
+          float* l_z = (split ? part_l(z + 1) : l) + r_off;
+          rc = step_stacked(c->dtype, static_cast<const unsigned char*>(q) + q_off * es, gk, gv, o_z, m_z,
+                            l_z, sh, make_posmap(qmap), km, seg_shard, seg_row, P, sloc, stride, flags,
+                            c->doc_len, st);
+          if (rc != RA_OK) return rc;
         }
-        const unsigned flags = split ? (causal_flag | RA_STEP_FRESH) : (causal_flag | RA_STEP_FINALIZE);
-        rc = step_stacked(c->dtype, q, buf_k[0], buf_v[0], split ? part_out(z + 1) : out,
-                          split ? part_m(z + 1) : m, split ? part_l(z + 1) : l, sh,
-                          make_posmap(qmap), km, seg_shard, seg_row, P, sloc, stride, flags,
-                          c->doc_len, st);
-        if (rc != RA_OK) return rc;
       }
       if (split) {
         for (int a = 0; a < kAuxStreams; ++a) {
