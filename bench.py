@@ -12,11 +12,16 @@ of the workload BASELINE.json's metric is quoted on:
 Metric: causal-adjusted attention TFLOP/s, FLOPs = 4 * B * H * S^2 * D / 2 (the reference's own
 model, apps/bench_attention/bench_attention.cu:46-51). `value` is the whole-job figure (all
 GPUs together, inputs resident in HBM); `e2e` is the same pass through the host-buffer entry
-point (host->device copies of Q/K/V and device->host copy of the output inside the timed
-region). At N=1 the line also carries the split-K decode measurement (tokens/s, HBM GB/s) for
-the decode workload (batch 4, 32 query / 8 KV heads, head_dim 128, 262144 cached tokens, fp16)
-and a CPU baseline: the reference's own cpu_attention (compiled unchanged into oracle/_ref)
-timed on this box's host cores on a bounded sample of the same workload.
+points of the C ABI (ra_prefill_host at N = 1, ra_ring_prefill_host at N > 1: host->device copies
+of Q/K/V and device->host copy of the output inside the timed region). `checked_rows`: output rows
+of every rank against the CPU oracle at full size, untimed, at every N. The line also carries
+the split-K decode measurement (tokens/s, HBM GB/s) for the decode workload (batch 4, 32 query /
+8 KV heads, head_dim 128, 262144 cached tokens, fp16; sharded over the ranks at N > 1, with one
+output row per batch element checked against the oracle), the other prefill workloads of the
+metric as secondary objects (`config5`: 131072 tokens per GPU, zig-zag-n 2, four documents, the
+1 M-token workload at N = 8; `config3`: GQA striped), and at N = 1 a CPU baseline: the
+reference's own cpu_attention (compiled unchanged into oracle/_ref) timed on this box's host
+cores on a bounded sample of the same workload.
 
 `--impl reference` times that CPU reference alone, on all host threads, on a bounded sample per
 step, and prints the same line with "impl": "reference".

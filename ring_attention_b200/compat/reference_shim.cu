@@ -183,6 +183,15 @@ void DeviceTensor<T>::copy_from_host(const T* host) {
 template <typename T>
 void DeviceTensor<T>::copy_to_host(T* host) const {
   cuda_must(cudaMemcpy(host, ptr_, bytes(), cudaMemcpyDeviceToHost), "copy_to_host");
+  // This is where results reach the caller: the reference would have aborted in cudaCheck had a
+  // kernel failed (src/common.cuh:16-24). A bounded device-side wait that ran out is this
+  // library's equivalent, so it aborts here too instead of handing back what the kernel left.
+  int st[4] = {0, 0, 0, 0};
+  if (ra_device_status(st) == RA_OK && st[0] != 0) {
+    std::fprintf(stderr, "copy_to_host: a device-side wait ran out (code %d, wait %d, block %d, tile %d)\n",
+                 st[0], st[1], st[2], st[3]);
+    std::abort();
+  }
 }
 template <typename T>
 void DeviceTensor<T>::copy_from_host(const std::vector<T>& host) {
