@@ -135,6 +135,17 @@ def test_ring_prefill_fp16_causal(layout, n_splits, schedule):
                      layout=layout, n_splits=n_splits, schedule=schedule))
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_gather_in_head_halves_with_split_keys(D):
+    # one batch row and MHA: the gather travels as two halves of the heads, each folded as it lands;
+    # few query blocks: the key segments are also split over two parallel launches and merged
+    world = _world()
+    _run(world, dict(kind="prefill", B=1, H=4, kvH=4, S=world * 2 * 256, D=D, causal=True, layout=1, n_splits=2,
+                     schedule="gather"))
+    _run(world, dict(kind="prefill", B=1, H=8, kvH=8, S=world * 4 * 128, D=D, causal=True, layout=1, n_splits=4,
+                     doc_len=world * 128, schedule="gather"))
+
+
 def test_ring_prefill_d128_noncausal_and_documents():
     world = _world()
     _run(world, dict(kind="prefill", B=2, H=4, kvH=4, S=world * 2 * 128, D=128, causal=False, layout=0, n_splits=2))
