@@ -94,7 +94,10 @@ RA_API int ra_attention_init(float* out, float* m, float* l, const ra_shape* sha
                              size_t m_count, ra_stream stream);
 
 /* One ring step, fp32 Q/K/V. Replaces launch_attention_step (src/attention.hpp:92-94,
- * src/attention_step.cu:488-525); seq_q == 1 dispatches to the decode kernel exactly as
+ * src/attention_step.cu:488-525). Head_dim 32, 64 and 128 run on the tensor cores with every
+ * operand split into two TF32 terms (about 2^-22 per product, inside the reference's fp32
+ * tolerance of 1e-5 for its test and benchmark inputs; RA_STEP_FORCE_SIMT of
+ * ra_attention_step_ex selects plain fp32), 256 on the SIMT kernel; seq_q == 1 dispatches to the decode kernel exactly as
  * the reference does (src/attention_step.cu:494-497). */
 RA_API int ra_attention_step(const float* q, const float* k, const float* v, float* out, float* m,
                              float* l, const ra_shape* shape, int q_offset, int k_offset,
@@ -137,7 +140,8 @@ RA_API int ra_attention_step_ex(int dtype, const void* q, const void* k, const v
 
 /* Which kernel the step entry points run for a dtype and head_dim (given 16-byte aligned
  * tensors): 1 = the tcgen05 / TMA / tensor-memory kernel (fp16 and bf16, head_dim 32, 64, 128,
- * 256), 0 = the SIMT fp32 kernel, -1 = unsupported. Host only. The reference dispatches on
+ * 256), 2 = the same on split TF32 operands (fp32, head_dim 32, 64, 128), 0 = the SIMT fp32
+ * kernel (fp32 head_dim 256, or any shape with RA_STEP_FORCE_SIMT), -1 = unsupported. Host only. The reference dispatches on
  * head_dim alone (src/attention_step_fp16.cu:275-292). */
 RA_API int ra_attention_step_path(int dtype, int head_dim);
 

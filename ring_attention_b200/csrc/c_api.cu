@@ -219,7 +219,7 @@ int ra_attention_step_stacked(int dtype, const void* q, const void* k, const voi
 RA_API int ra_attention_step_path(int dtype, int head_dim) {
   if (head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256) return -1;
   if (dtype == RA_F16 || dtype == RA_BF16) return 1;
-  if (dtype == RA_F32) return (head_dim == 32 || head_dim == 64) ? 2 : 0;
+  if (dtype == RA_F32) return head_dim <= 128 ? 2 : 0;
   return -1;
 }
 RA_API void ra_debug_set_wait_limit_ns(unsigned long long ns) { rab::set_tc_wait_limit_ns(ns); }

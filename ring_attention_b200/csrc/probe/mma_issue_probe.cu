@@ -66,6 +66,36 @@ __device__ inline void run_mn(unsigned tm, unsigned sbase, unsigned bar, unsigne
   parity ^= 1;
   if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { g_out[mode][0] = t1 - t0; g_out[mode][1] = t2 - t0; g_out[mode][2] = spins; }
 }
+
+// ---- kind::tf32 (K = 8 per instruction, 32-bit operands) ----
+__device__ inline void mma_ss_tf32(unsigned d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned acc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ inline void mma_ts_tf32(unsigned d, unsigned a, unsigned long long b, unsigned idesc, unsigned acc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+template <int N, bool TS>
+__device__ inline void run_tf32(unsigned tm, unsigned sbase, unsigned bar, unsigned& parity, int mode) {
+  const unsigned long long da = desc_kmajor(sbase);
+  const unsigned long long db = desc_kmajor(sbase + 16384);
+  constexpr unsigned idesc = make_idesc(2, 0, N, 128);
+  const long long t0 = clock64();
+#pragma unroll 8
+  for (int it = 0; it < kIters; ++it) {
+    const unsigned off = (it % 4) * 2;
+    if (elect_one()) {
+      if (TS) mma_ts_tf32(tm, tm + 448 + (it % 4) * 8, db + off, idesc, it > 0 ? 1u : 0u);
+      else mma_ss_tf32(tm, da + off, db + off, idesc, it > 0 ? 1u : 0u);
+    }
+  }
+  const long long t1 = clock64();
+  if (elect_one()) tc_commit(bar);
+  long long spins = 0;
+  while (!mbar_try_wait(bar, parity) && spins < 20000000) ++spins;
+  const long long t2 = clock64();
+  parity ^= 1;
+  if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { g_out[mode][0] = t1 - t0; g_out[mode][1] = t2 - t0; g_out[mode][2] = spins; }
+}
 template <int N, bool TS>
 __device__ inline void run_uniform(unsigned tm, unsigned sbase, unsigned bar, unsigned& parity, int mode) {
   // executed by all 32 lanes of one warp
@@ -139,6 +169,8 @@ __global__ void __launch_bounds__(128, 1) probe4(int dummy) {
     run_uniform<64, true>(tm, sbase, b, parity, 3);
     run_uniform<128, true>(tm, sbase, b, parity, 4);
     run_uniform<256, true>(tm, sbase, b, parity, 5);
+    run_tf32<64, false>(tm, sbase, b, parity, 14);
+    run_tf32<128, false>(tm, sbase, b, parity, 15);
     run_mn<64, true>(tm, sbase, b, parity, 10);
     run_mn<128, true>(tm, sbase, b, parity, 11);
     run_mn<64, false>(tm, sbase, b, parity, 12);
@@ -239,8 +271,8 @@ int main() {
   if (e != cudaSuccess) { printf("error %s\n", cudaGetErrorString(e)); return 1; }
   long long h[16][3];
   cudaMemcpyFromSymbol(h, g_out, sizeof(h));
-  const char* names[] = {"uniform SS N64", "uniform SS N128", "uniform SS N256", "uniform TS N64", "uniform TS N128", "uniform TS N256", "single SS N64", "single SS N128", "single TS N64", "single TS N128", "MN-major B TS N64", "MN-major B TS N128", "MN-major B SS N64", "MN-major B SS N128"};
-  for (int m = 0; m < 14; ++m)
+  const char* names[] = {"uniform SS N64", "uniform SS N128", "uniform SS N256", "uniform TS N64", "uniform TS N128", "uniform TS N256", "single SS N64", "single SS N128", "single TS N64", "single TS N128", "MN-major B TS N64", "MN-major B TS N128", "MN-major B SS N64", "MN-major B SS N128", "tf32 SS N64 (K=8)", "tf32 SS N128 (K=8)"};
+  for (int m = 0; m < 16; ++m)
     printf("  %-18s issue %6lld clk  done %6lld clk  = %.1f clk per MMA%s\n", names[m], h[m][0], h[m][1], h[m][1] / 64.0, h[m][2] >= 20000000 ? "  TIMEOUT" : "");
   cudaFuncSetAttribute(probe_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
   probe_pair<<<148, 128, 100 * 1024>>>(0);

@@ -5,17 +5,18 @@
 // of lo) is about 2^-22 of each product, unbiased, against the 2^-24 of an fp32 multiply-add: for
 // inputs of the reference's tests and benchmarks (N(0,1), U[-1,1)) the result meets the fp32
 // tolerance (1e-5) of the reference's fp32 step (src/attention_step.cu:114-282), which this
-// replaces for head_dim 32 and 64 at ~15x the speed of the SIMT kernel. Scores whose single
+// replaces for head_dim 32, 64 and 128 at ~15x the speed of the SIMT kernel. Scores whose single
 // products reach the hundreds lose that margin (error ~ 2^-22 * sum |q_d k_d| / sqrt(D) in the
-// exponent); RA_STEP_FORCE_SIMT selects the plain-fp32 kernel. Other head dims keep the SIMT
-// kernel.
+// exponent); RA_STEP_FORCE_SIMT selects the plain-fp32 kernel. Head_dim 256 keeps the SIMT kernel
+// (its Q tile and lo copy alone exceed shared memory).
 //
 // Work decomposition: grid = (batch * heads, 128-row query blocks); a block owns one 128-row
-// query tile and walks the visible 64-key tiles of every key segment, heaviest blocks first.
+// query tile and walks the visible 64-key tiles (32-key at head_dim 128) of every key segment,
+// heaviest blocks first.
 //
 // Roles inside a block (384 threads)
 //   warp 0        TMA producer: Q once, then K_t, V_t, K_t+1, ... as 128B-swizzled fp32 tiles into
-//                 a 4-slot shared-memory ring (no multicast).
+//                 a 4-slot (head_dim 128: 3-slot) shared-memory ring (no multicast).
 //   warp 1        MMA issuer (converged warp, one elected lane): S = Qh Kh^T + Ql Kh^T + Qh Kl^T
 //                 and O += Ph V_h + Pl V_h + Ph V_l, kind::tf32, accumulators in tensor memory.
 //   warps 4-7     splitter: when a raw tile has landed, rounds it to TF32 in place (hi) and writes
@@ -25,7 +26,7 @@
 //   S and P are double-buffered, so the scores of tile t+1 are computed while the softmax of
 //   tile t runs and the softmax of tile t+1 never waits for P.V of tile t.
 //
-// Tensor memory (columns): S0 [0,64) S1 [64,128) Ph0 Pl0 Ph1 Pl1 [128,384) O [384,384+D).
+// Tensor memory (columns, n = keys per tile): S0 S1 [0,2n) Ph0 Pl0 Ph1 Pl1 [2n,6n) O [6n,6n+D).
 // Every wait on an mbarrier is bounded (see tc_common.cuh); a wait that runs out reports into
 // the device status word and the block unwinds.
 #include "tc_common.cuh"
@@ -36,21 +37,25 @@ using namespace tcgen;
 
 namespace {
 
-constexpr int kBNf = 64;        // keys per tile
 constexpr int kThreadsF = 384;
-constexpr int kStagesF = 4;     // ring slots (raw + lo of one K or V tile each)
 
 template <int D>
 struct F32Cfg {
+  // head_dim 128: Q with its lo copy is 128 KiB, so the key tile shrinks to 32 keys and the ring
+  // to three slots (K_t, V_t and the K of the next tile) to fit beside it
+  static constexpr int kBN = D == 128 ? 32 : 64;        // keys per tile
+  static constexpr int kStages = D == 128 ? 3 : 4;      // ring slots (raw + lo of one K or V tile)
   static constexpr int kBoxes = D / 32;                 // 32 fp32 = one 128-byte box row
-  static constexpr int kQBytes = kBM * D * 4;           // one Q tile (raw or lo)
-  static constexpr int kKvBytes = kBNf * D * 4;         // one K or V tile (raw or lo)
-  static constexpr int kOffQ = 0;                       // raw, then lo
-  static constexpr int kOffKV = 2 * kQBytes;            // slot: raw, then lo
-  static constexpr int kOffBar = kOffKV + kStagesF * 2 * kKvBytes;
-  static constexpr int kNumBars = 2 + 3 * kStagesF + 8;
+  static constexpr int kQBytes = kBM * D * 4;           // one Q tile (hi or lo)
+  static constexpr int kKvBytes = kBN * D * 4;          // one K or V tile (hi or lo)
+  static constexpr int kOffQ = 0;                       // hi, then lo
+  static constexpr int kOffKV = 2 * kQBytes;            // slot: hi, then lo
+  static constexpr int kOffBar = kOffKV + kStages * 2 * kKvBytes;
+  static constexpr int kNumBars = 2 + 3 * kStages + 8;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
-  static constexpr int kColS = 0, kColP = 128, kColO = 384;
+  // tensor memory: S0 S1 (kBN columns each), Ph0 Pl0 Ph1 Pl1 (kBN each), O (D)
+  static constexpr int kColS = 0, kColP = 2 * kBN, kColO = 6 * kBN;
+  static_assert(kColO + D <= 512, "tensor memory budget");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
@@ -88,6 +93,8 @@ __global__ void __launch_bounds__(kThreadsF, 1)
                      const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const TcArgs a) {
   using C = F32Cfg<D>;
+  constexpr int kBNf = C::kBN;
+  constexpr int kStagesF = C::kStages;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -217,7 +224,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         tc_fence_after();
         const unsigned kv = s_kv + slot * 2 * C::kKvBytes;
         const unsigned long long kd_hi = desc_kmajor(kv), kd_lo = desc_kmajor(kv + C::kKvBytes);
-        const unsigned t_s = tmem_base + C::kColS + 64 * buf;
+        const unsigned t_s = tmem_base + C::kColS + kBNf * buf;
         if (elect_one()) {
 #pragma unroll
           for (int term = 0; term < 3; ++term) {
@@ -245,7 +252,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         // groups, 1 KiB) per k-step
         const unsigned long long vd_hi = desc_mnmajor_32b(kv, kBNf * 128, 512);
         const unsigned long long vd_lo = desc_mnmajor_32b(kv + C::kKvBytes, kBNf * 128, 512);
-        const unsigned t_ph = tmem_base + C::kColP + 128 * buf, t_pl = t_ph + 64;
+        const unsigned t_ph = tmem_base + C::kColP + 2 * kBNf * buf, t_pl = t_ph + kBNf;
         const unsigned t_o = tmem_base + C::kColO;
         if (elect_one()) {
 #pragma unroll
@@ -357,8 +364,8 @@ __global__ void __launch_bounds__(kThreadsF, 1)
       }
       for (int t = tr.lo; t < tr.hi && ok; ++t, ++j) {
         const int buf = j & 1;
-        const unsigned t_s = tmem_base + lane_base + C::kColS + 64 * buf;
-        const unsigned t_ph = tmem_base + lane_base + C::kColP + 128 * buf, t_pl = t_ph + 64;
+        const unsigned t_s = tmem_base + lane_base + C::kColS + kBNf * buf;
+        const unsigned t_ph = tmem_base + lane_base + C::kColP + 2 * kBNf * buf, t_pl = t_ph + kBNf;
         int c_lo = min(max(rel_lo - t * kBNf, 0), kBNf);
         int c_hi = min(max(rel_hi - t * kBNf, 0), kBNf);
         if (c_hi < c_lo) c_hi = c_lo;
@@ -369,15 +376,12 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         if (!ok) break;
         tc_fence_after();
         float s[kBNf];
-        {
-          float lo32[32], hi32[32];
-          tmem_ld32(t_s, lo32);
-          tmem_ld32(t_s + 32, hi32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            s[i] = lo32[i];
-            s[32 + i] = hi32[i];
-          }
+        for (int c = 0; c < kBNf / 32; ++c) {
+          float part[32];
+          tmem_ld32(t_s + 32 * c, part);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[32 * c + i] = part[i];
         }
         tc_fence_before();
         mbar_arrive(bar_s_free + 8 * buf);  // the tensor core may reuse this S buffer
@@ -398,7 +402,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         auto exponentials = [&](float neg_m) {
           float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < kBNf / 32; ++c) {
             float ph[32], pl[32];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
@@ -537,9 +541,9 @@ int launch_tf32(const StepArgs& a, cudaStream_t stream) {
   int rc = make_map(&mq, RA_F32, a.q, a.D, a.Sq, static_cast<long long>(a.B) * a.H,
                     static_cast<long long>(a.Sq) * a.D, kBM);
   if (rc != RA_OK) return rc;
-  rc = make_map(&mk, RA_F32, a.k, a.D, a.k_rows, a.k_heads_total, a.kv_head_stride, kBNf);
+  rc = make_map(&mk, RA_F32, a.k, a.D, a.k_rows, a.k_heads_total, a.kv_head_stride, C::kBN);
   if (rc != RA_OK) return rc;
-  rc = make_map(&mv, RA_F32, a.v, a.D, a.k_rows, a.k_heads_total, a.kv_head_stride, kBNf, true);
+  rc = make_map(&mv, RA_F32, a.v, a.D, a.k_rows, a.k_heads_total, a.kv_head_stride, C::kBN, true);
   if (rc != RA_OK) return rc;
   TcArgs t;
   t.out = a.out;
@@ -576,7 +580,7 @@ int launch_tf32(const StepArgs& a, cudaStream_t stream) {
 
 bool step_tf32_supported(int dtype, const StepArgs& a) {
   if (dtype != RA_F32) return false;
-  if (a.D != 32 && a.D != 64) return false;
+  if (a.D != 32 && a.D != 64 && a.D != 128) return false;
   if (a.Sq <= 0 || a.Sk <= 0) return false;
   if (a.qmap.n_seg * a.qmap.seg_len != a.Sq || a.kmap.n_seg * a.kmap.seg_len != a.Sk) return false;
   if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
@@ -587,7 +591,9 @@ bool step_tf32_supported(int dtype, const StepArgs& a) {
 
 int launch_step_tf32(const StepArgs& a, cudaStream_t stream) {
   RAB_REQUIRE(a.status != nullptr, RA_ERR_CUDA, "attention step: no device status word");
-  return a.D == 32 ? launch_tf32<32>(a, stream) : launch_tf32<64>(a, stream);
+  if (a.D == 32) return launch_tf32<32>(a, stream);
+  if (a.D == 64) return launch_tf32<64>(a, stream);
+  return launch_tf32<128>(a, stream);
 }
 
 }  // namespace rab

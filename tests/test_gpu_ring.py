@@ -136,9 +136,8 @@ def test_ring_prefill_fp16_causal(layout, n_splits, schedule):
 
 
 @pytest.mark.parametrize("D", [64, 128])
-def test_gather_in_head_halves_with_split_keys(D):
-    # one batch row and MHA: the gather travels as two halves of the heads, each folded as it lands;
-    # few query blocks: the key segments are also split over two parallel launches and merged
+def test_gather_with_split_keys_mha(D):
+    # few query blocks: the gathered key segments are split over two parallel launches and merged
     world = _world()
     _run(world, dict(kind="prefill", B=1, H=4, kvH=4, S=world * 2 * 256, D=D, causal=True, layout=1, n_splits=2,
                      schedule="gather"))

@@ -94,7 +94,7 @@ def test_fp32_step_reference_case_list(case):
     assert_close(lse, want_lse, 1e-5, 1e-5, "lse")
 
 
-@pytest.mark.parametrize("D", [32, 64])
+@pytest.mark.parametrize("D", [32, 64, 128])
 def test_fp32_tensor_core_and_simt_kernels_agree_with_the_oracle_at_1e5(D):
     # long rows, GQA, ragged lengths, end-aligned causal mask, inputs of mixed magnitudes: the
     # split-TF32 kernel (hi*hi + lo*hi + hi*lo) must hold the fp32 tolerance like the SIMT one
@@ -220,8 +220,8 @@ def test_every_reference_head_dim_takes_the_tensor_core_kernel_in_16_bit():
     for D in (32, 64, 128, 256):  # reference src/attention_step_fp16.cu:275-292
         assert lib().ra_attention_step_path(RA_F16, D) == 1
         assert lib().ra_attention_step_path(RA_BF16, D) == 1
-        # fp32: split-TF32 tensor-core kernel for head_dim 32 / 64, SIMT above
-        assert lib().ra_attention_step_path(RA_F32, D) == (2 if D <= 64 else 0)
+        # fp32: split-TF32 tensor-core kernel up to head_dim 128, SIMT for 256
+        assert lib().ra_attention_step_path(RA_F32, D) == (2 if D <= 128 else 0)
     assert lib().ra_attention_step_path(RA_F16, 48) == -1
 
 

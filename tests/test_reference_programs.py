@@ -45,14 +45,14 @@ def test_reference_gpu_programs(name, expect):
 
 # ---- the reference's MPI programs (its CTest smoke matrix, tests/CMakeLists.txt:22-60,108-177) ----
 
-def mpirun(n, prog, *args, timeout=600):
+def mpirun(n, prog, *args, timeout=600, extra_env=None):
     import torch
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
     launcher, path = os.path.join(BIN, "mpirun"), os.path.join(BIN, prog)
     if not (os.path.exists(launcher) and os.path.exists(path)):
         pytest.skip(f"{prog} was not built (oracle/_ref/tests is made where the reference tree is mounted)")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MINIMPI_TIMEOUT_S="120")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MINIMPI_TIMEOUT_S="120", **(extra_env or {}))
     # the launcher and its ranks get a process group of their own, so that a timeout can end all of
     # them (and only them) instead of leaving ranks behind with their communicators and GPUs
     proc = subprocess.Popen([launcher, "-n", str(n), path, *args], stdout=subprocess.PIPE,
@@ -86,6 +86,19 @@ def test_reference_cli_ring_smoke(n, mode, extra):
     import re
     out = mpirun(n, "ring_attention_cli", *SMOKE, *extra, "--mode", mode, "--verify")
     assert re.search(r"verify[^\n]*PASS", out), out[-1500:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,nodes", [(2, 2), (4, 2)])
+def test_reference_cli_ring_2d_in_two_tiers(n, nodes):
+    # the reference groups ranks by node (one node here); RA_RING2D_NODES makes the shim ask for
+    # several groups so that --mode ring-2d runs the two-tier order of Ring2DSchedule on one box
+    import re
+    out = mpirun(n, "ring_attention_cli", "--seq", "512", "--heads", "4", "--head_dim", "64", "--iters", "1",
+                 "--causal", "1", "--zigzag", "1", "--mode", "ring-2d", "--verify",
+                 extra_env={"RA_RING2D_NODES": str(nodes)})
+    assert re.search(r"verify[^
+]*PASS", out), out[-1500:]
 
 
 @pytest.mark.gpu
