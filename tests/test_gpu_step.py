@@ -215,6 +215,35 @@ def test_ragged_shapes_fp16(shape, causal):
     assert_close(got, want, 1e-3, 1e-3, "out")
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.float16, 64), (torch.float16, 128), (torch.float16, 256),
+                                     (torch.bfloat16, 64), (torch.float32, 64), (torch.float32, 128)])
+def test_scores_that_grow_along_the_keys_move_the_reference_point(dtype, D):
+    # The tensor-core kernels keep a row's reference point from tile to tile and move it only when
+    # a tile's row sum shows that some score ran far above it. Here the scores climb by ~24 in the
+    # exponent from one key tile to the next (and vary inside a tile), so that path, with its
+    # rescale of O and l and the recomputed tile, runs on almost every tile; rows of the second
+    # head fall instead, which never moves the reference.
+    S = 1024
+    rng = np.random.default_rng(11)
+    q = np.zeros((1, 2, 256, D), np.float32)
+    k = np.zeros((1, 2, S, D), np.float32)
+    q[..., 0] = 1.0
+    ramp = np.arange(S, dtype=np.float32) / 128.0 * 17.0 * np.sqrt(D)  # ~17 nats per 128 keys
+    k[0, 0, :, 0] = ramp / 4.0
+    k[0, 1, :, 0] = -ramp / 4.0
+    q[..., 0] = 4.0
+    q[..., 1:] = rng.standard_normal((1, 2, 256, D - 1)).astype(np.float32) * 0.3
+    k[..., 1:] = rng.standard_normal((1, 2, S, D - 1)).astype(np.float32) * 0.3
+    v = rng.standard_normal((1, 2, S, D)).astype(np.float32)
+    q, k, v = (round_to(x, dtype) for x in (q, k, v))
+    want, want_lse = oracle.cpu_attention(q, k, v, True, want_lse=True)
+    qmap, kmap = SegMap.make([S - 256], 256), SegMap.make([0], S)
+    got, lse = run_ex(q, k, v, qmap, kmap, 1, True, dtype, 2)
+    tol = TOL[dtype]
+    assert_close(got, want, tol, tol, "out")
+    assert_close(lse, want_lse, tol * 10 if dtype == torch.float32 else tol, tol, "lse")
+
+
 def test_every_reference_head_dim_takes_the_tensor_core_kernel_in_16_bit():
     from ring_attention_b200._lib import RA_BF16, RA_F16, RA_F32, lib
     for D in (32, 64, 128, 256):  # reference src/attention_step_fp16.cu:275-292
