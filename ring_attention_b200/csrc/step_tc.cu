@@ -65,27 +65,6 @@ constexpr int kBN = 128;           // keys per tile
 #define RAB_REGS_LO 72
 #define RAB_REGS_HI 216
 #endif
-#ifdef RAB_POLY_EVERY
-// 2^x for two lanes on the FMA pipe: n = round(x) through the 1.5 * 2^23 rounding constant,
-// 2^(x - n) by a degree-3 polynomial on [-0.5, 0.5] (max relative error 7.5e-5, below the
-// 2.4e-4 rounding of 16-bit P), n added to the exponent bits; x clamped at -125.
-__device__ inline float2 exp2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -125.f);
-  x.y = fmaxf(x.y, -125.f);
-  const float2 magic = make_float2(12582912.f, 12582912.f);
-  const float2 t = fadd2(x, magic);
-  const float2 n = fadd2(t, make_float2(-12582912.f, -12582912.f));
-  const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
-  float2 p = ffma2(f, make_float2(0.0551716685f, 0.0551716685f),
-                   make_float2(0.2426111251f, 0.2426111251f));
-  p = ffma2(p, f, make_float2(0.6932609677f, 0.6932609677f));
-  p = ffma2(p, f, make_float2(0.9999280572f, 0.9999280572f));
-  float2 r;
-  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
-  return r;
-}
-#endif
 template <bool kBf16>
 __device__ inline unsigned pack16(float lo, float hi) {
 
@@ -492,11 +471,7 @@ __global__ void __launch_bounds__((TcCfg<D, kPInTmem>::kThreads), 1)
             const float2 x0 = ffma2(make_float2(s[c], s[c + 1]), scale2, negm2);
             const float2 x1 = ffma2(make_float2(s[c + 2], s[c + 3]), scale2, negm2);
             const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
-#ifdef RAB_POLY_EVERY
-            const float2 p1 = ((i / 4) % RAB_POLY_EVERY == 0) ? exp2_poly2(x1) : make_float2(ex2(x1.x), ex2(x1.y));
-#else
             const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
-#endif
             sum_a = fadd2(sum_a, p0);
             sum_b = fadd2(sum_b, p1);
             pk[i / 2] = pack16<kBf16>(p0.x, p0.y);

@@ -239,9 +239,11 @@ def test_scores_that_grow_along_the_keys_move_the_reference_point(dtype, D):
     want, want_lse = oracle.cpu_attention(q, k, v, True, want_lse=True)
     qmap, kmap = SegMap.make([S - 256], 256), SegMap.make([0], S)
     got, lse = run_ex(q, k, v, qmap, kmap, 1, True, dtype, 2)
-    tol = TOL[dtype]
+    # fp32: the raw scores reach ~1000, where one fp32 ulp of the score is already 1e-4 (1.5e-5 in
+    # the exponent after scaling), so two correct fp32 summation orders differ by more than 1e-5
+    tol = 1e-4 if dtype == torch.float32 else TOL[dtype]
     assert_close(got, want, tol, tol, "out")
-    assert_close(lse, want_lse, tol * 10 if dtype == torch.float32 else tol, tol, "lse")
+    assert_close(lse, want_lse, tol, tol, "lse")
 
 
 def test_every_reference_head_dim_takes_the_tensor_core_kernel_in_16_bit():
