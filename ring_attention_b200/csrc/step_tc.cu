@@ -91,6 +91,12 @@ struct TcCfg {
   static constexpr int kItemBytes = kTileBytes / kItemsPerTile;
   static constexpr int kStages = D == 256 ? (kPInTmem ? 10 : 8)
                                           : (kPInTmem ? (D == 128 ? 4 : 6) : (D == 128 ? 3 : 6));
+  // Item-wise K/V (head_dim 256): K items and V items get a ring half each. In one shared ring
+  // of 1.25 tiles the K items of tile t+1 would wait for slots that P.V of tile t-1 frees last, and
+  // their load latency would sit in front of every score tile; with a half each, K(t+1) loads as
+  // soon as the scores of tile t are done and V(t) as soon as P.V of tile t-1 is, both under the
+  // softmax of tile t.
+  static constexpr bool kSplitRing = kItemsPerTile > 1;
   static constexpr int kPBytes = kPInTmem ? 0 : kBM * kBN * 2;
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = kTiles * kTileBytes;
@@ -115,6 +121,23 @@ struct TcCfg {
   static_assert(kItemsPerTile == 1 || kEarlyS, "item-wise K/V needs the early-S schedule");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
+
+// Where a K (which = 0) or V (which = 1) item of key tile t sits in the ring and how often that
+// slot has been used before (its barrier phase).
+struct RingPos {
+  int slot, use;
+};
+template <class C>
+__device__ inline RingPos ring_pos(int which, int t, int sub) {
+  if constexpr (C::kSplitRing) {
+    constexpr int kHalf = C::kStages / 2;
+    const int n = t * C::kItemsPerTile + sub;
+    return {which * kHalf + n % kHalf, n / kHalf};
+  } else {
+    const int it = (2 * t + which) * C::kItemsPerTile + sub;
+    return {it % C::kStages, it / C::kStages};
+  }
+}
 
 
 // DR is the head_dim of the tensors in memory: D, or 32 on the 64-wide kernel (see launch_cfg).
@@ -220,35 +243,50 @@ __global__ void __launch_bounds__((TcCfg<D, kPInTmem>::kThreads), 1)
           tma_load_3d(s_q + w * C::kTileBytes + bx * (kBM * 128), &tmap_q, bar_q_full + 8 * w,
                       bx * 64, q_row + w * kBM, bh);
       }
-      int it = 0;
+      int it = 0, jt = 0;  // ring items and key tiles so far
       bool ok = true;
+      // all ring items of one operand (which: 0 = K, 1 = V) of key tile `tile`
+      auto load_items = [&](int which, int tile, int k_row, int k_head) {
+        for (int sub = 0; sub < C::kItemsPerTile && ok; ++sub, ++it) {
+          const RingPos pos = ring_pos<C>(which, tile, sub);
+          const int slot = pos.slot;
+          if (pos.use >= 1)
+            ok = mbar_wait(bar_kv_empty + 8 * slot, (pos.use + 1) & 1, abort_flag, a.status, 1, it,
+                           a.wait_ns);
+          if (!ok) break;
+          // test hook: stop feeding the ring so that a consumer's bounded wait runs out
+          if (a.stall_after >= 0 && it >= a.stall_after) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(bar_kv_full + 8 * slot, C::kItemBytes);
+          const CUtensorMap* map = which == 0 ? &tmap_k : &tmap_v;
+          for (int bx = 0; bx < C::kBoxesPerItem; ++bx)
+            tma_load_3d(s_kv + slot * C::kItemBytes + bx * (kBN * 128), map, bar_kv_full + 8 * slot,
+                        (sub * C::kBoxesPerItem + bx) * 64, k_row, k_head);
+        }
+      };
+      // Order of the loads. One ring: K(t), V(t), K(t+1), ... (the order the slots come free in).
+      // Two half rings: K(0), K(1), V(0), K(2), V(1), ... - the issuer runs the scores of tile
+      // t + 1 before P.V of tile t, so K(t+1) must not queue behind a V(t) that waits for P.V of
+      // tile t - 1.
+      int v_row = 0, v_head = 0;
+      bool v_pending = false;
       for (int sk = 0; sk < a.kmap.n_seg && ok; ++sk) {
         const TileRange r = tile_range<kBN>(a.kmap, sk, a.stride, causal, a.doc_len, qmin, qmax);
-        for (int t = r.lo; t < r.hi && ok; ++t) {
+        for (int t = r.lo; t < r.hi && ok; ++t, ++jt) {
           const int k_row = a.kseg_row[sk] + t * kBN;
           const int k_head = a.kseg_head[sk] + kv_bh;
-          // ring items of this tile: K (all its items), then V; item = kBoxesPerItem boxes
-          for (int sub = 0; sub < 2 * C::kItemsPerTile && ok; ++sub, ++it) {
-            const int which = sub / C::kItemsPerTile;
-            const int box0 = (sub % C::kItemsPerTile) * C::kBoxesPerItem;
-            const int slot = it % C::kStages;
-            if (it >= C::kStages)
-              ok = mbar_wait(bar_kv_empty + 8 * slot, ((it / C::kStages) + 1) & 1, abort_flag,
-                             a.status, 1, it, a.wait_ns);
-            if (!ok) break;
-            // test hook: stop feeding the ring so that a consumer's bounded wait runs out
-            if (a.stall_after >= 0 && it >= a.stall_after) {
-              ok = false;
-              break;
-            }
-            mbar_expect_tx(bar_kv_full + 8 * slot, C::kItemBytes);
-            const CUtensorMap* map = which == 0 ? &tmap_k : &tmap_v;
-            for (int bx = 0; bx < C::kBoxesPerItem; ++bx)
-              tma_load_3d(s_kv + slot * C::kItemBytes + bx * (kBN * 128), map,
-                          bar_kv_full + 8 * slot, (box0 + bx) * 64, k_row, k_head);
+          load_items(0, jt, k_row, k_head);
+          if constexpr (C::kSplitRing) {
+            if (v_pending) load_items(1, jt - 1, v_row, v_head);
+            v_row = k_row, v_head = k_head, v_pending = true;
+          } else {
+            load_items(1, jt, k_row, k_head);
           }
         }
       }
+      if (C::kSplitRing && v_pending && ok) load_items(1, jt - 1, v_row, v_head);
     }
   } else if (warp == 1 || (warp == 2 && C::kTiles == 2)) {
     // ------------------------------------------------------------- MMA issuers ----
@@ -280,10 +318,10 @@ __global__ void __launch_bounds__((TcCfg<D, kPInTmem>::kThreads), 1)
         return __all_sync(0xffffffffu,
                           mbar_wait(bar, parity, abort_flag, a.status, which, tile, a.wait_ns)) != 0;
       };
-      auto wait_kv = [&](int it, int which, int tile) {
-        return wait(bar_kv_full + 8 * (it % C::kStages), (it / C::kStages) & 1, which, tile);
+      auto wait_kv = [&](RingPos pos, int which, int tile) {
+        return wait(bar_kv_full + 8 * pos.slot, pos.use & 1, which, tile);
       };
-      // Ring items of key tile t: K items [2t * kIPT, ...), V items [(2t + 1) * kIPT, ...).
+      // Ring items of key tile t: see ring_pos.
       // The k-steps of one K item of S_w = Q_w K^T (called by the elected lane).
       auto s_ksteps = [&](int slot, int sub) {
         const unsigned long long kd = dkv0_k + static_cast<unsigned long long>(slot * kItemUnits);
@@ -315,8 +353,9 @@ __global__ void __launch_bounds__((TcCfg<D, kPInTmem>::kThreads), 1)
         bool good = true;
 #pragma unroll
         for (int sub = 0; sub < kIPT && good; ++sub) {
-          const int it = 2 * t * kIPT + sub, slot = it % C::kStages;
-          good = wait_kv(it, 5, t);
+          const RingPos pos = ring_pos<C>(0, t, sub);
+          const int slot = pos.slot;
+          good = wait_kv(pos, 5, t);
           if (!good) break;
           tc_fence_after();
           if (elect_one()) {
@@ -332,8 +371,9 @@ __global__ void __launch_bounds__((TcCfg<D, kPInTmem>::kThreads), 1)
         bool good = true;
 #pragma unroll
         for (int sub = 0; sub < kIPT && good; ++sub) {
-          const int it = (2 * t + 1) * kIPT + sub, slot = it % C::kStages;
-          good = wait_kv(it, 4, t);
+          const RingPos pos = ring_pos<C>(1, t, sub);
+          const int slot = pos.slot;
+          good = wait_kv(pos, 4, t);
           if (!good) break;
           tc_fence_after();
           if (elect_one()) {
@@ -358,9 +398,9 @@ __global__ void __launch_bounds__((TcCfg<D, kPInTmem>::kThreads), 1)
           // P aliases S (whole tiles are single ring items here): P.V of tile t and the scores
           // of tile t+1 go out in one batch once P_w(t) is written; the scores' completion
           // tells the softmax group that P.V is done as well.
-          const int it_v = 2 * t + 1, it_k = 2 * t + 2;
-          const int slot_v = it_v % C::kStages, slot_k = it_k % C::kStages;
-          ok = wait_kv(it_v, 4, t) && (!more || wait_kv(it_k, 5, t)) && wait(b_p_full, t & 1, 6, t);
+          const RingPos pos_v = ring_pos<C>(1, t, 0), pos_k = ring_pos<C>(0, t + 1, 0);
+          const int slot_v = pos_v.slot, slot_k = pos_k.slot;
+          ok = wait_kv(pos_v, 4, t) && (!more || wait_kv(pos_k, 5, t)) && wait(b_p_full, t & 1, 6, t);
           if (!ok) break;
           tc_fence_after();
           if (elect_one()) {
