@@ -125,6 +125,9 @@ RA_API int ra_attention_step_segmented(const float* q, const float* k, const flo
 #define RA_STEP_FORCE_SIMT 8u /* run the SIMT kernel whatever the head_dim (cross-checks) */
 #define RA_STEP_P_IN_SMEM 16u /* tcgen05 kernel: stage P through shared memory instead of tensor
                                * memory (the second, cross-checking form of the same kernel) */
+#define RA_STEP_CTA_PAIR 32u /* tcgen05 kernel, head_dim 128 / 256 with P in tensor memory: cluster
+                              * pairs with M = 256 MMAs (cta_group::2), each block holding half of
+                              * every K / V tile; the third, cross-checking form of the kernel */
 
 /* The general step every other step entry point funnels into: any dtype, segmented
  * positions with a stride, optional document mask (visible only if

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libring_attention_b200.so")
 RA_F32, RA_F16, RA_BF16 = 0, 1, 2
 RA_STEP_CAUSAL, RA_STEP_FRESH, RA_STEP_FINALIZE, RA_STEP_FORCE_SIMT = 1, 2, 4, 8
 RA_STEP_P_IN_SMEM = 16
+RA_STEP_CTA_PAIR = 32
 RA_MAX_SEG = 16
 
 STATUS_NAMES = {0: "RA_OK", 1: "RA_ERR_INVALID", 2: "RA_ERR_CUDA", 3: "RA_ERR_UNSUPPORTED",

@@ -89,12 +89,14 @@ def launch_attention_step_segmented(q, k, v, out, m, l, shape, qmap: SegMap, kma
 
 def attention_step_ex(q, k, v, out, m, l, shape, qmap, kmap, pos_stride=1, causal=False,
                       fresh=False, finalize=False, force_simt=False, doc_len=0, kv_row_stride=0,
-                      p_in_smem=False):
+                      p_in_smem=False, cta_pair=False):
     """General step: any dtype, segment maps with a stride, document mask, fused init/finalize.
-    ``p_in_smem`` selects the tcgen05 kernel's second form (P staged through shared memory)."""
+    ``p_in_smem`` selects the tcgen05 kernel's second form (P staged through shared memory),
+    ``cta_pair`` its cluster-pair form (M = 256 MMAs over two blocks; head_dim 128 / 256)."""
     flags = ((RA_STEP_CAUSAL if causal else 0) | (RA_STEP_FRESH if fresh else 0) |
              (RA_STEP_FINALIZE if finalize else 0) | (RA_STEP_FORCE_SIMT if force_simt else 0) |
-             (_lib.RA_STEP_P_IN_SMEM if p_in_smem else 0))
+             (_lib.RA_STEP_P_IN_SMEM if p_in_smem else 0) |
+             (_lib.RA_STEP_CTA_PAIR if cta_pair else 0))
     check(lib().ra_attention_step_ex(_dtype(q), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(m),
                                      _ptr(l), C.byref(shape.c()), C.byref(qmap), C.byref(kmap),
                                      pos_stride, flags, doc_len, kv_row_stride, _stream()))

@@ -44,6 +44,19 @@ __device__ inline bool mbar_try_wait(unsigned bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
+// The same with acquire semantics at cluster scope: for a barrier that threads of the peer CTA of
+// a pair arrive on.
+__device__ inline bool mbar_try_wait_cluster(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Non-blocking form: has the phase with this parity completed?
 __device__ inline bool mbar_test_wait(unsigned bar, unsigned parity) {
   unsigned ok;
@@ -74,13 +87,17 @@ __device__ inline unsigned long long global_ns() {
 
 // Bounded wait. Returns false when the block is aborting (own limit reached or another
 // role flagged it). `which` identifies the wait in the status word.
+template <bool kClusterScope = false>
 __device__ inline bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag,
                                  int* status, int which, int tile, unsigned long long limit_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
+  auto try_wait = [&]() {
+    return kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
+  };
+  if (try_wait()) return true;
   const unsigned long long t0 = global_ns();
   unsigned spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (try_wait()) return true;
     if ((++spins & 255u) == 0) {
       if (*abort_flag) return false;
       if (global_ns() - t0 > limit_ns) {
@@ -133,6 +150,55 @@ __device__ inline void mma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long lo
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+
+// ---- CTA pairs (cta_group::2): one instruction drives the tensor cores of two CTAs of a cluster,
+// M = 256 (128 rows from each CTA's A operand and into each CTA's tensor memory), each CTA
+// holding half of the B operand's N columns in its own shared memory at the same offset.
+__device__ inline unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ inline void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
+                   : "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ inline void mbar_arrive_cluster(unsigned bar, unsigned rank) {
+  asm volatile(
+      "{\n\t.reg .b32 r;\n\t"
+      "mapa.shared::cluster.u32 r, %0, %1;\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [r];\n\t}" ::"r"(bar),
+      "r"(rank)
+      : "memory");
+}
+// The barrier at this offset in BOTH CTAs of the pair gets the arrival.
+__device__ inline void tc_commit_pair(unsigned bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(bar),
+      "h"(static_cast<unsigned short>(3))
+      : "memory");
+}
+__device__ inline void mma_ss_pair(unsigned d_tmem, unsigned long long a_desc,
+                                   unsigned long long b_desc, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ inline void mma_ts_pair(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc,
+                                   unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }

@@ -120,13 +120,13 @@ def test_config1_fp32_noncausal_mha_output_and_lse():
 
 
 def run_ex(q, k, v, qmap, kmap, stride, causal, dtype, kvH, doc_len=0, force_simt=False,
-           p_in_smem=False):
+           p_in_smem=False, cta_pair=False):
     B, H, Sq, D = q.shape
     out, m, l = state(B, H, Sq, D, poison=True)
     api.attention_step_ex(dev(q, dtype), dev(k, dtype), dev(v, dtype), out, m, l,
                           api.AttentionShape(B, H, Sq, k.shape[2], D, kvH), qmap, kmap, stride,
                           causal=causal, fresh=True, finalize=True, doc_len=doc_len,
-                          force_simt=force_simt, p_in_smem=p_in_smem)
+                          force_simt=force_simt, p_in_smem=p_in_smem, cta_pair=cta_pair)
     torch.cuda.synchronize()
     assert api.device_status()[0] == 0
     return out.cpu().numpy(), api.attention_lse(m, l).cpu().numpy()
@@ -265,9 +265,38 @@ def test_head_dim_256_long_rows_both_kernels_agree_with_the_oracle(dtype):
     want = oracle.cpu_attention(q, k, v, True, kv_heads=2)
     qmap, kmap = SegMap.make([1100 - 300], 300), SegMap.make([0], 1100)
     tol = 1e-3 if dtype == torch.float16 else 8e-3
-    for kwargs in ({}, {"p_in_smem": True}, {"force_simt": True}):
+    for kwargs in ({}, {"p_in_smem": True}, {"cta_pair": True}, {"force_simt": True}):
         got, _ = run_ex(q, k, v, qmap, kmap, 1, True, dtype, 2, **kwargs)
         assert_close(got, want, tol, tol, f"D=256 {dtype} {kwargs}")
+
+
+@pytest.mark.parametrize("D", [128, 256])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_cluster_pair_form_of_the_tensor_core_kernel(D, dtype):
+    """M = 256 MMAs over two blocks of a cluster (cta_group::2): each block loads half of every
+    K / V tile. Odd numbers of query blocks (the last pair's second block has no rows), a single
+    block per segment (falls back to independent blocks), zig-zag segments, GQA, causal and
+    document masks; the result must also equal the independent-block form bit for bit."""
+    tol = 1e-3 if dtype == torch.float16 else 8e-3
+    for seed, (Sq, Sk, causal, doc_len) in enumerate([(640, 1408, True, 0), (1200, 1200, True, 0),
+                                                      (130, 700, False, 0), (900, 900, True, 200),
+                                                      (1024, 2048, False, 0)]):
+        q, k, v = normal_inputs(500 + seed + D, 1, 4, 2, Sq, Sk, D, scale=0.8)
+        q, k, v = (round_to(x, dtype) for x in (q, k, v))
+        qmap, kmap = SegMap.make([Sk - Sq], Sq), SegMap.make([0], Sk)
+        want, _ = masked_truth(q, k, v, positions(qmap, 1), positions(kmap, 1), causal, doc_len, 2) \
+            if doc_len else (oracle.cpu_attention(q, k, v, causal, kv_heads=2), None)
+        pair, lse_pair = run_ex(q, k, v, qmap, kmap, 1, causal, dtype, 2, doc_len=doc_len, cta_pair=True)
+        single, lse_single = run_ex(q, k, v, qmap, kmap, 1, causal, dtype, 2, doc_len=doc_len)
+        assert_close(pair, want, tol, tol, f"D={D} Sq={Sq} Sk={Sk} causal={causal} doc={doc_len}")
+        assert np.array_equal(pair, single) and np.array_equal(lse_pair, lse_single)
+    # zig-zag: two query segments and four key segments with their own bases
+    q, k, v = normal_inputs(611 + D, 1, 2, 1, 2 * 384, 4 * 384, D, scale=0.8)
+    q, k, v = (round_to(x, dtype) for x in (q, k, v))
+    qmap, kmap = SegMap.make([384, 6 * 384], 384), SegMap.make([0, 384, 6 * 384, 7 * 384], 384)
+    want, _ = masked_truth(q, k, v, positions(qmap, 1), positions(kmap, 1), True, 0, 1)
+    pair, _ = run_ex(q, k, v, qmap, kmap, 1, True, dtype, 1, cta_pair=True)
+    assert_close(pair, want, tol, tol, f"D={D} zig-zag")
 
 
 @pytest.mark.parametrize("p_in_smem", [False, True])
