@@ -561,7 +561,9 @@ def run_profile_case(args):
     """A small, self-ending case for `ncu`: few launches, at most ~1 GB on the device.
     prefill: the benchmark's own shape (100 MB of Q/K/V, larger than L2 together with the 67 MB
     output), 1 warm-up + 2 launches of the step kernel. decode: the decode workload at a
-    quarter of the cached length (65536 tokens, 1 GB of K/V), 1 warm-up + 2 steps."""
+    quarter of the cached length (65536 tokens, 1 GB of K/V), 1 warm-up + 2 steps.
+    prefill-d128 / prefill-d256 / prefill-d256-pair: the step kernel's other head_dims (and its
+    cluster-pair form) on B1 H8 S16384 causal (0.4 GB on the device)."""
     import torch
 
     from ring_attention_b200 import api
@@ -569,7 +571,19 @@ def run_profile_case(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(42)
-    if args.profile == "prefill":
+    if args.profile.startswith("prefill-d"):
+        D = 128 if "128" in args.profile else 256
+        B, H, S = 1, 8, 16384
+        q, k, v = (torch.randn((B, H, S, D), generator=g, device=dev, dtype=torch.float16) for _ in range(3))
+        out = torch.empty((B, H, S, D), device=dev)
+        m = torch.empty((B, H, S), device=dev)
+        l = torch.empty_like(m)
+        one = SegMap.make([0], S)
+        for _ in range(3):
+            api.attention_step_ex(q, k, v, out, m, l, api.AttentionShape(B, H, S, S, D), one, one, 1,
+                                  causal=True, fresh=True, finalize=True,
+                                  cta_pair=args.profile.endswith("pair"))
+    elif args.profile == "prefill":
         w = WORKLOAD
         B, H, S, D = w["batch"], w["heads"], w["seq"], w["head_dim"]
         q, k, v = (torch.randn((B, H, S, D), generator=g, device=dev, dtype=torch.float16) for _ in range(3))
@@ -695,7 +709,7 @@ def check_decode_rows(torch, dist, dev, cache, lens, q, out, rank, P):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "prefill-d128", "prefill-d256", "prefill-d256-pair"],
                     help="run a small self-ending case for ncu instead of the benchmark")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
