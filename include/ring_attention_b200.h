@@ -85,6 +85,10 @@ RA_API int ra_device_status(int out[4]);
  * RA_ERR_DEVICE_WAIT, nothing is accessed out of bounds. Process-wide; not for production use. */
 RA_API void ra_debug_set_wait_limit_ns(unsigned long long ns);
 RA_API void ra_debug_stall_producer_after(int items);
+/* Block order of the tcgen05 step kernel: -1 = chosen by shape (default), 0 = (batch, head)
+ * fastest, 1 = all query blocks of the heads sharing a KV head before the next KV head. Lets a
+ * test run either order on a small shape. Process-wide; not for production use. */
+RA_API void ra_debug_set_block_order(int order);
 
 /* ------------------------------------------------------------------ prefill ---- */
 

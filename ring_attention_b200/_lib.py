@@ -146,6 +146,7 @@ _SIG = {
     "ra_attention_step_path": (C.c_int, [C.c_int, C.c_int]),
     "ra_debug_set_wait_limit_ns": (None, [C.c_ulonglong]),
     "ra_debug_stall_producer_after": (None, [C.c_int]),
+    "ra_debug_set_block_order": (None, [C.c_int]),
 }
 
 _lib = None

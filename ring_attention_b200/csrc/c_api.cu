@@ -11,6 +11,7 @@ namespace rab {
 
 void set_tc_wait_limit_ns(unsigned long long ns);
 void set_tc_stall_after(int items);
+void set_tc_block_order(int order);
 
 namespace {
 
@@ -224,6 +225,7 @@ RA_API int ra_attention_step_path(int dtype, int head_dim) {
 }
 RA_API void ra_debug_set_wait_limit_ns(unsigned long long ns) { rab::set_tc_wait_limit_ns(ns); }
 RA_API void ra_debug_stall_producer_after(int items) { rab::set_tc_stall_after(items); }
+RA_API void ra_debug_set_block_order(int order) { rab::set_tc_block_order(order); }
 
 
 /* ------------------------------------------------ whole attention, device buffers ---- */

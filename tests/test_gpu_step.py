@@ -299,6 +299,29 @@ def test_cluster_pair_form_of_the_tensor_core_kernel(D, dtype):
     assert_close(pair, want, tol, tol, f"D={D} zig-zag")
 
 
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_both_block_orders_of_the_tensor_core_kernel(D):
+    """Heads fastest (default) and all query blocks of the heads of one KV head first (default only
+    for grouped KV heads with very many query blocks): same results bit for bit, GQA with two
+    batches, zig-zag query segments, with and without cluster pairs."""
+    from ring_attention_b200._lib import lib
+    q, k, v = normal_inputs(900 + D, 2, 6, 2, 2 * 320, 4 * 320, D, scale=0.8)
+    q, k, v = (round_to(x, torch.float16) for x in (q, k, v))
+    qmap, kmap = SegMap.make([320, 6 * 320], 320), SegMap.make([0, 320, 6 * 320, 7 * 320], 320)
+    want, _ = masked_truth(q, k, v, positions(qmap, 1), positions(kmap, 1), True, 0, 2)
+    got = {}
+    try:
+        for order in (0, 1):
+            lib().ra_debug_set_block_order(order)
+            for pair in ((False, True) if D >= 128 else (False,)):
+                got[order, pair] = run_ex(q, k, v, qmap, kmap, 1, True, torch.float16, 2, cta_pair=pair)
+    finally:
+        lib().ra_debug_set_block_order(-1)
+    for key, (out, lse) in got.items():
+        assert_close(out, want, 1e-3, 1e-3, f"D={D} order/pair={key}")
+        assert np.array_equal(out, got[0, False][0]) and np.array_equal(lse, got[0, False][1]), key
+
+
 @pytest.mark.parametrize("p_in_smem", [False, True])
 def test_both_p_paths_of_the_tensor_core_kernel(p_in_smem):
     for D in (32, 64, 128, 256):
