@@ -892,14 +892,21 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.stall_after = g_stall_after.load(std::memory_order_relaxed);
   const long long n_qblocks = static_cast<long long>(t.n_qblocks_per_seg) * a.qmap.n_seg;
   // Block order. By default the (batch, head) index runs fastest and the query blocks go heavy
-  // first over the whole grid, which balances best. With grouped KV heads and at least 512 query
-  // blocks per KV head the other order wins (measured B2 H32/kvH8 S32768 D128, 4 x 128 blocks per
-  // KV head: 1105 -> 1155 TFLOP/s; the same at S131072: 310 -> 242 ms per pass): all
-  // query blocks of the heads that share one KV head, heavy first, before the next KV head - the
-  // blocks in flight then read a single K/V stream from its first key on. With few blocks per
-  // head that order loses to its per-head tails (H8 S8192 D64: 589 -> 409).
+  // first over the whole grid, which balances best. With at least 512 query blocks per KV head
+  // (query heads sharing it times blocks of a head; a document mask cuts a head into independent
+  // pieces of doc_len rows) the other order wins: all query blocks of the heads that share one
+  // KV head, heavy first, before the next KV head. The blocks in flight then read a single K/V
+  // stream from its first key on, DRAM traffic and with it power drop and the SM clock rises.
+  // Measured, D128 causal: B2 H32/kvH8 S131072 271 -> 241 ms per pass (SM clock 1350 -> 1550 MHz
+  // under the power cap), B2 H32/kvH8 S32768 1105 -> 1155 TFLOP/s, H16 MHA S131072 1110 -> 1165;
+  // with fewer blocks per KV head it loses to its per-head tails (H16 MHA S131072 in four documents
+  // 1118 -> 1095, H8 S8192 D64 589 -> 409).
   const int order = g_block_order.load(std::memory_order_relaxed);
-  t.heads_outer = order >= 0 ? order : (a.kvH < a.H && (a.H / a.kvH) * n_qblocks >= 512 ? 1 : 0);
+  const long long rows_eff = a.doc_len > 0 && a.doc_len < a.qmap.seg_len * static_cast<long long>(a.qmap.n_seg)
+                                 ? a.doc_len
+                                 : static_cast<long long>(a.qmap.seg_len) * a.qmap.n_seg;
+  const long long blocks_per_kv_head = (a.H / a.kvH) * ((rows_eff + kQBlock - 1) / kQBlock);
+  t.heads_outer = order >= 0 ? order : (blocks_per_kv_head >= 512 ? 1 : 0);
   const long long bh_total = static_cast<long long>(a.B) * a.H;
   RAB_REQUIRE((t.heads_outer ? bh_total : n_qblocks) <= 65535, RA_ERR_INVALID,
               "attention step: grid too large (%lld query blocks, %lld heads)", n_qblocks, bh_total);
