@@ -7,8 +7,15 @@
 //
 // Work decomposition
 //   grid = (batch * heads, query blocks). A block owns 256 query rows of one segment as two
-//   128-row tiles and walks the visible 128-key tiles of every key segment.
-//   Heaviest query blocks (largest positions) are launched first.
+//   128-row tiles (head_dim 256: one tile) and walks the visible 128-key tiles of every key
+//   segment. Heaviest query blocks (largest positions) are launched first; with very many query
+//   blocks per KV head the grid is turned so that all query blocks of the heads sharing one KV
+//   head run before the next KV head (see launch_cfg).
+//
+// Three selectable forms of the same kernel, tested against each other: P in tensor memory
+// (default) or staged through shared memory (RA_STEP_P_IN_SMEM), and cluster pairs
+// (RA_STEP_CTA_PAIR, head_dim 128 / 256): tcgen05.mma.cta_group::2 with M = 256 over the two
+// blocks of a cluster, each block loading half of every K and V tile.
 //
 // Roles inside a block (384 threads)
 //   warp 0        TMA producer: Q tiles once, then K_j, V_j, K_j+1, ... into a shared-memory
@@ -29,6 +36,7 @@
 //
 // Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D), and
 // at head_dim 64 a separate P0 / P1 of 64 columns each behind them (otherwise P overwrites S).
+// Head_dim 256: S0 / S1 are the two score buffers of the one query tile, O takes [256,512).
 //
 // What bounds it: a timing probe of back-to-back tcgen05.mma from an elected lane gives 66 clk
 // per M128 N128 K16 instruction (shared-memory operands) and 33 clk at N = 64 with A in tensor
