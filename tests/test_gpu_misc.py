@@ -115,14 +115,17 @@ def _small_causal_case(seed=3, S=1024, D=64, H=2):
     return q, k, v, oracle.cpu_attention(q, k, v, True)
 
 
-def test_bounded_wait_runs_out_and_the_context_stays_usable():
+@pytest.mark.parametrize("D,cta_pair", [(64, False), (256, False), (128, True)])
+def test_bounded_wait_runs_out_and_the_context_stays_usable(D, cta_pair):
     """The tcgen05 kernel's waits are bounded: with the TMA producer told to stop after the
     first K/V tiles and the limit set to a few milliseconds, the kernel returns by itself, the
     status word says which wait gave up, host entry points that synchronise report
-    RA_ERR_DEVICE_WAIT, and after the word is read (which clears it) the same launch is right."""
+    RA_ERR_DEVICE_WAIT, and after the word is read (which clears it) the same launch is right.
+    Covers the three schedules of the kernel (head_dim 64, 256) and its cluster-pair form, where
+    both blocks of a pair have to give up and meet at the cluster barrier."""
     from ring_attention_b200._lib import RingAttentionError, lib
     L = lib()
-    S, D, H = 1024, 64, 2
+    S, H = 1024, 2
     q, k, v, want = _small_causal_case(S=S, D=D, H=H)
     dq, dk, dv = (dev(x, torch.float16) for x in (q, k, v))
     out = torch.zeros((1, H, S, D), device="cuda")
@@ -134,7 +137,8 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable():
     L.ra_debug_set_wait_limit_ns(5_000_000)
     L.ra_debug_stall_producer_after(2)
     try:
-        api.attention_step_ex(dq, dk, dv, out, m, l, shape, one, one, causal=True, fresh=True, finalize=True)
+        api.attention_step_ex(dq, dk, dv, out, m, l, shape, one, one, causal=True, fresh=True, finalize=True,
+                              cta_pair=cta_pair)
         torch.cuda.synchronize()  # returns: nothing waits forever
         # a host-buffer entry point synchronises, so it reports the failure itself
         hq, hk, hv = (torch.from_numpy(x).to(torch.float16).pin_memory() for x in (q, k, v))
@@ -150,7 +154,8 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable():
     status = api.device_status()  # reads and clears
     assert status[0] == 5 and status[1] > 0, status
     assert api.device_status()[0] == 0
-    api.attention_step_ex(dq, dk, dv, out, m, l, shape, one, one, causal=True, fresh=True, finalize=True)
+    api.attention_step_ex(dq, dk, dv, out, m, l, shape, one, one, causal=True, fresh=True, finalize=True,
+                          cta_pair=cta_pair)
     torch.cuda.synchronize()
     assert api.device_status()[0] == 0
     assert_close(out.cpu().numpy(), want, 1e-3, 1e-3, "after the status word was cleared")
