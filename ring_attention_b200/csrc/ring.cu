@@ -21,6 +21,7 @@
 #include <dlfcn.h>
 #include <nvtx3/nvToolsExt.h>
 
+#include <algorithm>
 #include <mutex>
 #include <vector>
 
@@ -126,6 +127,8 @@ constexpr int kMaxKeyParts = 7;  // + the own-shard state = the 8 states one mer
 
 using namespace rab;
 
+constexpr int kHostGroupsMax = 2;  // head groups of the pipelined host pass
+
 struct ra_ring {
   int rank, cp;
   ncclComm_t comm;
@@ -143,8 +146,9 @@ struct ra_ring {
   // host-buffer pass (ra_ring_prefill_host): device staging, grown on demand
   void* host_buf;
   size_t host_bytes;
-  cudaStream_t host_stream, host_q_stream;
+  cudaStream_t host_stream, host_q_stream, host_out_stream;
   cudaEvent_t ev_host_q, ev_host_begin, ev_host_end;
+  cudaEvent_t ev_host_up[kHostGroupsMax], ev_host_done[kHostGroupsMax], ev_host_pass;  // head-group pipeline of the host pass
 };
 
 static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
@@ -164,6 +168,12 @@ static int ring_finish_create(int rank, int cp, ncclComm_t comm, bool own, ra_ri
   RAB_CUDA(cudaEventCreateWithFlags(&r->ev_host_q, cudaEventDisableTiming));
   RAB_CUDA(cudaEventCreate(&r->ev_host_begin));
   RAB_CUDA(cudaEventCreate(&r->ev_host_end));
+  RAB_CUDA(cudaStreamCreateWithFlags(&r->host_out_stream, cudaStreamNonBlocking));
+  RAB_CUDA(cudaEventCreate(&r->ev_host_pass));
+  for (int i = 0; i < kHostGroupsMax; ++i) {
+    RAB_CUDA(cudaEventCreateWithFlags(&r->ev_host_up[i], cudaEventDisableTiming));
+    RAB_CUDA(cudaEventCreateWithFlags(&r->ev_host_done[i], cudaEventDisableTiming));
+  }
   // The transfer stream gets the highest priority: the step kernel keeps every SM full (one
   // block per SM, all registers), so the few blocks of a send/recv kernel can only run on SMs
   // the block scheduler hands them first. Without the priority they queue behind the step
@@ -248,9 +258,16 @@ void ra_ring_destroy(ra_ring* r) {
   if (r->dec_buf) cudaFree(r->dec_buf);
   cudaStreamSynchronize(r->host_stream);
   cudaStreamSynchronize(r->host_q_stream);
+  cudaStreamSynchronize(r->host_out_stream);
   if (r->host_buf) cudaFree(r->host_buf);
   cudaStreamDestroy(r->host_stream);
   cudaStreamDestroy(r->host_q_stream);
+  cudaStreamDestroy(r->host_out_stream);
+  cudaEventDestroy(r->ev_host_pass);
+  for (int i = 0; i < kHostGroupsMax; ++i) {
+    cudaEventDestroy(r->ev_host_up[i]);
+    cudaEventDestroy(r->ev_host_done[i]);
+  }
   cudaEventDestroy(r->ev_host_q);
   cudaEventDestroy(r->ev_host_begin);
   cudaEventDestroy(r->ev_host_end);
@@ -760,7 +777,27 @@ int ra_ring_prefill_host(ra_ring* r, const ra_ring_config* c, const void* q_host
   const size_t kv_raw = static_cast<size_t>(c->batch) * kvH * sloc * c->head_dim * es;
   const size_t out_bytes = rows * c->head_dim * sizeof(float);
   const size_t lse_bytes = rows * sizeof(float);
-  const size_t work_bytes = ra_ring_prefill_workspace_bytes(r, c);
+  // (see below) two half passes over head groups, when the heads are independent slices
+  // Measured on config 2 (75 MB up per pass over the P links, 8 heads): N = 2 2.45 -> 1.94 ms with
+  // two groups (three or four: 2.00), N = 4 no difference (1.72-1.83 against 1.77-1.84, 25 MB per
+  // rank); below 16 MB per rank the second pass's own latency is not worth it.
+  const int n_groups =
+      (c->batch == 1 && kvH == c->heads && c->heads >= 2 && q_bytes + 2 * kv_raw >= (16u << 20))
+          ? kHostGroupsMax
+          : 1;
+  const bool two_groups = n_groups >= 2;
+  int h_split[kHostGroupsMax + 1];
+  for (int g = 0; g <= n_groups; ++g) h_split[g] = static_cast<int>(static_cast<long long>(c->heads) * g / n_groups);
+  size_t work_bytes = ra_ring_prefill_workspace_bytes(r, c);
+  if (two_groups) {
+    // a half pass may pick another plan (more key parts for fewer blocks): take the largest need
+    work_bytes = 0;
+    for (int g = 0; g < n_groups; ++g) {
+      ra_ring_config cg = *c;
+      cg.heads = cg.kv_heads = h_split[g + 1] - h_split[g];
+      work_bytes = std::max(work_bytes, ra_ring_prefill_workspace_bytes(r, &cg));
+    }
+  }
   const size_t need = align256(q_bytes) + 2 * align256(kv_raw) + align256(out_bytes) +
                       align256(lse_bytes) + align256(work_bytes);
   if (r->host_bytes < need) {
@@ -786,8 +823,72 @@ int ra_ring_prefill_host(ra_ring* r, const ra_ring_config* c, const void* q_host
   p += align256(lse_bytes);
   void* work = p;
   cudaStream_t st = r->host_stream;
-  // K and V go first: the transfers of the pass (all-gather or first hop) need only them and
-  // start while Q is still on its way up on a second stream; the first step waits for Q.
+  // One KV head per query head and one batch element: the heads are independent, contiguous
+  // slices of every tensor, so the pass runs as two half passes (head groups) in a pipeline -
+  // upload of the second half under the first half's pass, download of the first half under
+  // the second half's pass. Each half pass pays its own transfers' latency, which the copies
+  // it hides outweigh when a rank moves tens of megabytes.
+  if (two_groups) {
+    cudaStream_t up = r->host_q_stream, down = r->host_out_stream;
+    const size_t head_elems = sloc * c->head_dim;
+    RAB_CUDA(cudaEventRecord(r->ev_host_begin, st));
+    RAB_CUDA(cudaStreamWaitEvent(up, r->ev_host_begin, 0));
+    for (int g = 0; g < n_groups; ++g) {
+      const size_t off = h_split[g] * head_elems * es, n = (h_split[g + 1] - h_split[g]) * head_elems * es;
+      RAB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(dk) + off, static_cast<const unsigned char*>(k_host) + off, n, cudaMemcpyHostToDevice, up));
+      RAB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(dv) + off, static_cast<const unsigned char*>(v_host) + off, n, cudaMemcpyHostToDevice, up));
+      RAB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(dq) + off, static_cast<const unsigned char*>(q_host) + off, n, cudaMemcpyHostToDevice, up));
+      RAB_CUDA(cudaEventRecord(r->ev_host_up[g], up));
+    }
+    for (int g = 0; g < n_groups; ++g) {
+      const int hg = h_split[g + 1] - h_split[g];
+      const size_t off = h_split[g] * head_elems, row_off = h_split[g] * sloc;
+      ra_ring_config cg = *c;
+      cg.heads = hg;
+      cg.kv_heads = hg;
+      RAB_CUDA(cudaStreamWaitEvent(st, r->ev_host_up[g], 0));
+      if (g == 0) RAB_CUDA(cudaEventRecord(r->ev_host_pass, st));
+      rc = ring_prefill_impl(r, &cg, static_cast<unsigned char*>(dq) + off * es,
+                             static_cast<unsigned char*>(dk) + off * es,
+                             static_cast<unsigned char*>(dv) + off * es, dout + off,
+                             lse_host ? dlse + row_off : nullptr, work, work_bytes, st, nullptr, nullptr);
+      if (rc != RA_OK) {
+        cudaStreamSynchronize(up);
+        cudaStreamSynchronize(st);
+        cudaStreamSynchronize(r->comm_stream);
+        cudaStreamSynchronize(down);
+        return rc;
+      }
+      RAB_CUDA(cudaEventRecord(r->ev_host_done[g], st));
+      RAB_CUDA(cudaStreamWaitEvent(down, r->ev_host_done[g], 0));
+      RAB_CUDA(cudaMemcpyAsync(out_host + off, dout + off, hg * head_elems * sizeof(float),
+                               cudaMemcpyDeviceToHost, down));
+      if (lse_host)
+        RAB_CUDA(cudaMemcpyAsync(lse_host + row_off, dlse + row_off, hg * sloc * sizeof(float),
+                                 cudaMemcpyDeviceToHost, down));
+    }
+    RAB_CUDA(cudaEventRecord(r->ev_host_end, down));
+    rc = enqueue_status_read(st);
+    if (rc != RA_OK) return rc;
+    RAB_CUDA(cudaStreamSynchronize(down));
+    RAB_CUDA(cudaStreamSynchronize(st));
+    RAB_CUDA(cudaStreamSynchronize(r->comm_stream));
+    rc = status_after_sync();
+    if (rc != RA_OK) return rc;
+    if (result) {
+      float ms = 0.f, pass_ms = 0.f;
+      RAB_CUDA(cudaEventElapsedTime(&ms, r->ev_host_begin, r->ev_host_end));
+      RAB_CUDA(cudaEventElapsedTime(&pass_ms, r->ev_host_pass, r->ev_end));
+      result->total_ms = ms;           // upload + both half passes + download
+      result->comp_ms = pass_ms;       // first half pass's start to second half pass's end
+      result->comm_ms = 0.0;
+      result->wait_ms = ms - pass_ms;  // time on the host link not covered by the passes
+    }
+    return RA_OK;
+  }
+  // Otherwise one pass. K and V go first: the transfers of the pass (all-gather or first hop)
+  // need only them and start while Q is still on its way up on a second stream; the first step
+  // waits for Q.
   RAB_CUDA(cudaEventRecord(r->ev_host_begin, st));
   RAB_CUDA(cudaMemcpyAsync(dk, k_host, kv_raw, cudaMemcpyHostToDevice, st));
   RAB_CUDA(cudaMemcpyAsync(dv, v_host, kv_raw, cudaMemcpyHostToDevice, st));

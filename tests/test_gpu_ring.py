@@ -35,7 +35,20 @@ def _worker(rank, world, port, case, ret):
             part = api.RingPartition(world, rank, S, case["layout"], case["n_splits"])
             rows = part.local_positions()
             ql, kl, vl = (t[:, :, rows].contiguous().cuda() for t in (q, k, v))
-            for _ in range(2):  # twice: buffers and events are reused across passes
+            if case.get("host"):
+                # host-buffer entry point: pinned shards in, pinned output out
+                hq, hk, hv = (t[:, :, rows].contiguous().pin_memory() for t in (q, k, v))
+                out = torch.empty((B, H, len(rows), D), dtype=torch.float32).pin_memory()
+                lse = torch.empty((B, H, len(rows)), dtype=torch.float32).pin_memory()
+                for _ in range(2):
+                    out.fill_(float("nan"))
+                    res = ring.prefill_host(hq, hk, hv, out, seq=S, causal=case["causal"], layout=case["layout"],
+                                            n_splits=case["n_splits"], lse=lse,
+                                            schedule=case.get("schedule", "auto"), timed=True)
+                _, want_lse = oracle.cpu_attention(q.float().numpy(), k.float().numpy(), v.float().numpy(),
+                                                   case["causal"], kv_heads=kvH, want_lse=True)
+                assert np.abs(lse.numpy() - want_lse[:, :, rows.numpy()]).max() < 2e-3
+            for _ in range(0 if case.get("host") else 2):  # twice: buffers and events are reused across passes
                 out, lse, res = ring.prefill(ql, kl, vl, seq=S, causal=case["causal"], layout=case["layout"],
                                              n_splits=case["n_splits"], doc_len=case.get("doc_len", 0),
                                              want_lse=True, timed=True,
@@ -174,6 +187,18 @@ def test_ring_blocking_and_2d_schedules(layout, n_splits):
     _run(world, dict(base, schedule="blocking"))
     for nodes in sorted({1, 2, world}):  # one group, two groups, every rank its own group
         _run(world, dict(base, schedule="ring2d", nodes=nodes))
+
+
+@pytest.mark.parametrize("schedule", ["auto", "ring"])
+def test_ring_prefill_from_host_buffers(schedule):
+    """ra_ring_prefill_host: one pass below the size where the pass is pipelined over two head
+    groups, and above it with an even and an odd number of heads."""
+    world = _world()
+    _run(world, dict(kind="prefill", host=True, B=1, H=4, kvH=4, S=world * 2 * 128, D=64, causal=True, layout=1,
+                     n_splits=2, schedule=schedule))
+    for H in (16, 15):  # 18.9 / 17.7 MB of Q, K, V per rank: two head groups of 8 + 8 / 7 + 8 heads
+        _run(world, dict(kind="prefill", host=True, B=1, H=H, kvH=H, S=world * 2 * 768, D=128, causal=True,
+                         layout=1, n_splits=2, schedule=schedule))
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16"])
