@@ -393,7 +393,10 @@ RA_API int ra_ring_prefill_plan(const ra_ring* r, const ra_ring_config* cfg, int
 /* The same pass from HOST buffers holding this rank's shards (pinned memory recommended): K and
  * V are uploaded first so that the pass's transfers start while Q is still on its way, the
  * output (and lse, if not NULL) comes back to the host, and the call returns after everything
- * has completed. Device staging lives in the ring handle and grows on demand. The reference
+ * has completed. With one KV head per query head, batch 1 and at least 16 MB of Q, K, V per rank
+ * the pass runs as two half passes over head groups instead, so that the second half's upload
+ * and the first half's download overlap a pass (every rank takes the same decision from cfg).
+ * Device staging lives in the ring handle and grows on demand. The reference
  * uploads inside its timed pass too (src/ring_loop_fp16.cu:624-626). `result`, if not NULL,
  * gets total_ms = upload + pass + download, comp_ms = the pass alone, wait_ms = the rest.
  * Returns RA_ERR_DEVICE_WAIT when a bounded device-side wait ran out during the pass. */
