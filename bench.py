@@ -573,7 +573,8 @@ def run_profile_case(args):
     output), 1 warm-up + 2 launches of the step kernel. decode: the decode workload at a
     quarter of the cached length (65536 tokens, 1 GB of K/V), 1 warm-up + 2 steps.
     prefill-d128 / prefill-d256 / prefill-d256-pair: the step kernel's other head_dims (and its
-    cluster-pair form) on B1 H8 S16384 causal (0.4 GB on the device)."""
+    cluster-pair form) on B1 H8 S16384 causal (0.4 GB on the device). prefill-gqa /
+    prefill-gqa-heads-fastest: B2 H32/kvH8 S32768 D128 causal in either block order."""
     import torch
 
     from ring_attention_b200 import api
@@ -581,7 +582,24 @@ def run_profile_case(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(42)
-    if args.profile.startswith("prefill-d"):
+    if args.profile.startswith("prefill-gqa"):
+        # grouped KV heads, 512 query blocks per KV head: the shape class of config 3 at a quarter
+        # of its length (2 GB on the device), in the kernel's default block order for it (all
+        # query blocks of the heads of one KV head first) or with (batch, head) fastest
+        B, H, kvH, S, D = 2, 32, 8, 32768, 128
+        q = torch.randn((B, H, S, D), generator=g, device=dev, dtype=torch.float16)
+        k, v = (torch.randn((B, kvH, S, D), generator=g, device=dev, dtype=torch.float16) for _ in range(2))
+        out = torch.empty((B, H, S, D), device=dev)
+        m = torch.empty((B, H, S), device=dev)
+        l = torch.empty_like(m)
+        one = SegMap.make([0], S)
+        if args.profile.endswith("heads-fastest"):
+            api.lib().ra_debug_set_block_order(0)
+        for _ in range(3):
+            api.attention_step_ex(q, k, v, out, m, l, api.AttentionShape(B, H, S, S, D, kvH), one, one, 1,
+                                  causal=True, fresh=True, finalize=True)
+        api.lib().ra_debug_set_block_order(-1)
+    elif args.profile.startswith("prefill-d"):
         D = 128 if "128" in args.profile else 256
         B, H, S = 1, 8, 16384
         q, k, v = (torch.randn((B, H, S, D), generator=g, device=dev, dtype=torch.float16) for _ in range(3))
@@ -719,7 +737,8 @@ def check_decode_rows(torch, dist, dev, cache, lens, q, out, rank, P):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "prefill-d128", "prefill-d256", "prefill-d256-pair"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "prefill-d128", "prefill-d256", "prefill-d256-pair", "prefill-gqa",
+                             "prefill-gqa-heads-fastest"],
                     help="run a small self-ending case for ncu instead of the benchmark")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
