@@ -582,7 +582,18 @@ def run_profile_case(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(42)
-    if args.profile.startswith("prefill-gqa"):
+    if args.profile == "prefill-docs":
+        # one query head per KV head, four documents: config 5's shard on one GPU (2.7 GB)
+        B, H, S, D, doc = 1, 16, 131072, 128, 32768
+        q, k, v = (torch.randn((B, H, S, D), generator=g, device=dev, dtype=torch.float16) for _ in range(3))
+        out = torch.empty((B, H, S, D), device=dev)
+        m = torch.empty((B, H, S), device=dev)
+        l = torch.empty_like(m)
+        one = SegMap.make([0], S)
+        for _ in range(3):
+            api.attention_step_ex(q, k, v, out, m, l, api.AttentionShape(B, H, S, S, D), one, one, 1,
+                                  causal=True, fresh=True, finalize=True, doc_len=doc)
+    elif args.profile.startswith("prefill-gqa"):
         # grouped KV heads, 512 query blocks per KV head: the shape class of config 3 at a quarter
         # of its length (2 GB on the device), in the kernel's default block order for it (all
         # query blocks of the heads of one KV head first) or with (batch, head) fastest
@@ -738,7 +749,7 @@ def check_decode_rows(torch, dist, dev, cache, lens, q, out, rank, P):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile", default=None, choices=["prefill", "decode", "prefill-d128", "prefill-d256", "prefill-d256-pair", "prefill-gqa",
-                             "prefill-gqa-heads-fastest"],
+                             "prefill-gqa-heads-fastest", "prefill-docs"],
                     help="run a small self-ending case for ncu instead of the benchmark")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

@@ -86,8 +86,9 @@ RA_API int ra_device_status(int out[4]);
 RA_API void ra_debug_set_wait_limit_ns(unsigned long long ns);
 RA_API void ra_debug_stall_producer_after(int items);
 /* Block order of the tcgen05 step kernel: -1 = chosen by shape (default), 0 = (batch, head)
- * fastest, 1 = all query blocks of the heads sharing a KV head before the next KV head. Lets a
- * test run either order on a small shape. Process-wide; not for production use. */
+ * fastest, k > 0 = waves of k KV heads (all query blocks of their query heads before the next
+ * k; ignored unless k divides batch * kv_heads). Lets a test run every order on a small shape.
+ * Process-wide; not for production use. */
 RA_API void ra_debug_set_block_order(int order);
 
 /* ------------------------------------------------------------------ prefill ---- */

@@ -214,14 +214,18 @@ __global__ void __launch_bounds__((TcCfg<D, kPInTmem, kPair>::kThreads), 1)
   // (pairs: the two blocks of a cluster are neighbours in x - the pair instructions want the
   // cluster laid out along x - so x = 2 * (batch*head) + rank and y counts pairs of query blocks)
   int bh, qb_lin;
-  if (a.heads_outer) {
-    // x = query block (heavy first; the two blocks of a pair are neighbours), y = head, the
-    // query heads that share a KV head next to each other: the blocks in flight read ONE K/V
-    // stream, all from its first key on and at the same pace.
-    qb_lin = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-    const int group = a.H / a.kvH, y = static_cast<int>(blockIdx.y);
-    const int kv_lin = y / group;  // batch * kvH + kv head
-    bh = (kv_lin / a.kvH) * a.H + (y % group) * a.kvH + kv_lin % a.kvH;
+  if (a.kv_per_wave > 0) {
+    // Waves of KV heads: y = a set of kv_per_wave KV heads, x = (query block, heavy first) x (the
+    // query heads of that set, fastest). The blocks in flight read the K/V streams of one set
+    // only, all from their first key on and at the same pace. (Pairs: the two blocks of a
+    // cluster, neighbours in x, take the query blocks 2i and 2i + 1 of one head.)
+    const int group = a.H / a.kvH, per_x = group * a.kv_per_wave;
+    const int n_qb = a.n_qblocks_per_seg * a.qmap.n_seg;
+    const int x = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int j = x % per_x;
+    qb_lin = kPair ? n_qb - 1 - (2 * (x / per_x) + static_cast<int>(blockIdx.x & 1)) : n_qb - 1 - x / per_x;
+    const int kv_lin = static_cast<int>(blockIdx.y) * a.kv_per_wave + j / group;  // batch * kvH + kv head
+    bh = (kv_lin / a.kvH) * a.H + (j % group) * a.kvH + kv_lin % a.kvH;
   } else {
     bh = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     qb_lin = kPair ? 2 * static_cast<int>(gridDim.y) - 1 -
@@ -861,7 +865,7 @@ __global__ void __launch_bounds__((TcCfg<D, kPInTmem, kPair>::kThreads), 1)
 // Test hooks (see ra_debug_set_wait_limit_ns / ra_debug_stall_producer_after).
 std::atomic<unsigned long long> g_wait_ns{kWaitLimitNs};
 std::atomic<int> g_stall_after{-1};
-std::atomic<int> g_block_order{-1};  // -1: by shape, 0: heads inner, 1: heads outer
+std::atomic<int> g_block_order{-1};  // -1: by shape, 0: heads fastest, k > 0: waves of k KV heads
 
 template <int D, bool kBf16, bool kPInTmem, int DR, bool kPair = false>
 int launch_cfg(const StepArgs& a, cudaStream_t stream) {
@@ -899,24 +903,45 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
   t.wait_ns = g_wait_ns.load(std::memory_order_relaxed);
   t.stall_after = g_stall_after.load(std::memory_order_relaxed);
   const long long n_qblocks = static_cast<long long>(t.n_qblocks_per_seg) * a.qmap.n_seg;
-  // Block order. By default the (batch, head) index runs fastest and the query blocks go heavy
-  // first over the whole grid, which balances best. With at least 512 query blocks per KV head
-  // (query heads sharing it times blocks of a head; a document mask cuts a head into independent
-  // pieces of doc_len rows) the other order wins: all query blocks of the heads that share one
-  // KV head, heavy first, before the next KV head. The blocks in flight then read a single K/V
-  // stream from its first key on, DRAM traffic and with it power drop and the SM clock rises.
-  // Measured, D128 causal: B2 H32/kvH8 S131072 271 -> 241 ms per pass (SM clock 1350 -> 1550 MHz
-  // under the power cap), B2 H32/kvH8 S32768 1105 -> 1155 TFLOP/s, H16 MHA S131072 1110 -> 1165;
-  // with fewer blocks per KV head it loses to its per-head tails (H16 MHA S131072 in four documents
-  // 1118 -> 1095, H8 S8192 D64 589 -> 409).
-  const int order = g_block_order.load(std::memory_order_relaxed);
-  const long long rows_eff = a.doc_len > 0 && a.doc_len < a.qmap.seg_len * static_cast<long long>(a.qmap.n_seg)
-                                 ? a.doc_len
-                                 : static_cast<long long>(a.qmap.seg_len) * a.qmap.n_seg;
-  const long long blocks_per_kv_head = (a.H / a.kvH) * ((rows_eff + kQBlock - 1) / kQBlock);
-  t.heads_outer = order >= 0 ? order : (blocks_per_kv_head >= 512 ? 1 : 0);
+  // Block order. By default (kv_per_wave = 0) the (batch, head) index runs fastest and the query
+  // blocks go heavy first over the whole grid, which balances best - as long as the K and V of
+  // all heads stay in L2 together. When they do not (long sequences: 67 MB per KV head at
+  // S131072 D128), every block streams its keys from DRAM, and on the long head_dim 128 passes,
+  // which run under the power cap, that traffic costs clock. Then the grid is cut into waves of
+  // KV heads: all query blocks (heavy first) of the query heads of a few KV heads, whose K/V
+  // (the part a block sweeps: a document, if there is a mask) fit in about half of L2, before
+  // the next few - but never fewer than 512 blocks per wave, or the waves' tails cost more than
+  // the traffic. Measured on D128 causal, same GPU: B2 H32/kvH8 S131072 271 -> 241 ms per pass
+  // (SM clock 1350 -> 1550 MHz; at S32768 DRAM reads 12.4 -> 0.81 GB per launch, the algorithmic
+  // bytes), H16 MHA S131072 1110 -> 1165 TFLOP/s; one head at a time with fewer blocks loses
+  // (H16 MHA S131072 in four documents 1118 -> 1095, H8 S8192 D64 589 -> 409).
+  const long long kv_heads_total = static_cast<long long>(a.B) * a.kvH;
+  const long long q_rows = static_cast<long long>(a.qmap.seg_len) * a.qmap.n_seg;
+  const long long k_rows = static_cast<long long>(a.kmap.seg_len) * a.kmap.n_seg;
+  const long long q_rows_eff = a.doc_len > 0 && a.doc_len < q_rows ? a.doc_len : q_rows;
+  const long long k_rows_eff = a.doc_len > 0 && a.doc_len < k_rows ? a.doc_len : k_rows;
+  const long long kv_bytes_per_head = k_rows_eff * a.D * 2 * 2;  // K and V, 16-bit
+  const long long blocks_per_kv_head = (a.H / a.kvH) * ((q_rows_eff + kQBlock - 1) / kQBlock);
+  int kv_per_wave = 0;
+  if (kv_bytes_per_head * kv_heads_total > (96ll << 20)) {
+    auto divisor_at_most = [&](long long want) {
+      long long d = std::max(1ll, std::min(want, kv_heads_total));
+      while (kv_heads_total % d) --d;
+      return d;
+    };
+    long long d = divisor_at_most((64ll << 20) / std::max(1ll, kv_bytes_per_head));
+    while (d < kv_heads_total && d * blocks_per_kv_head < 512) {
+      ++d;
+      while (kv_heads_total % d) ++d;
+    }
+    kv_per_wave = d < kv_heads_total ? static_cast<int>(d) : 0;
+  }
+  const int order = g_block_order.load(std::memory_order_relaxed);  // test hook
+  if (order == 0 || (order > 0 && kv_heads_total % order == 0)) kv_per_wave = order;
+  t.kv_per_wave = kv_per_wave;
   const long long bh_total = static_cast<long long>(a.B) * a.H;
-  RAB_REQUIRE((t.heads_outer ? bh_total : n_qblocks) <= 65535, RA_ERR_INVALID,
+  const long long per_x = kv_per_wave > 0 ? static_cast<long long>(a.H / a.kvH) * kv_per_wave : 0;
+  RAB_REQUIRE(kv_per_wave > 0 ? n_qblocks * per_x < (1ll << 31) : n_qblocks <= 65535, RA_ERR_INVALID,
               "attention step: grid too large (%lld query blocks, %lld heads)", n_qblocks, bh_total);
   auto kern = step_tc_kernel<D, kBf16, kPInTmem, DR, kPair>;
   // once per device and instantiation: the attribute call costs microseconds that a pass of a
@@ -929,11 +954,12 @@ int launch_cfg(const StepArgs& a, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) smem_set.fetch_or(1ull << dev, std::memory_order_release);
   }
   dim3 grid(static_cast<unsigned>(a.B) * a.H, static_cast<unsigned>(n_qblocks));
-  if (t.heads_outer) grid = dim3(static_cast<unsigned>(n_qblocks), static_cast<unsigned>(a.B) * a.H);
+  if (kv_per_wave > 0)
+    grid = dim3(static_cast<unsigned>(n_qblocks * per_x), static_cast<unsigned>(kv_heads_total / kv_per_wave));
   if constexpr (kPair) {
     // the two blocks of a pair are neighbours in x; they take the query blocks 2i and 2i + 1
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = t.heads_outer ? grid : dim3(2 * grid.x, grid.y / 2);
+    cfg.gridDim = kv_per_wave > 0 ? grid : dim3(2 * grid.x, grid.y / 2);
     cfg.blockDim = dim3(C::kThreads);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;

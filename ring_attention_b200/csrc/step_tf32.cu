@@ -546,7 +546,7 @@ int launch_tf32(const StepArgs& a, cudaStream_t stream) {
   rc = make_map(&mv, RA_F32, a.v, a.D, a.k_rows, a.k_heads_total, a.kv_head_stride, C::kBN, true);
   if (rc != RA_OK) return rc;
   TcArgs t;
-  t.heads_outer = 0;
+  t.kv_per_wave = 0;
   t.out = a.out;
   t.m = a.m;
   t.l = a.l;

@@ -403,7 +403,7 @@ struct TcArgs {
   int* status;
   unsigned long long wait_ns;  // limit of every device-side wait
   int stall_after;             // test hook: the producer stops after this many ring items (< 0: off)
-  int heads_outer;             // block order: all query blocks of a head before the next head
+  int kv_per_wave;             // block order: waves of this many KV heads (0: heads fastest)
 };
 
 // ---- host side ----------------------------------------------------------------------

@@ -301,9 +301,9 @@ def test_cluster_pair_form_of_the_tensor_core_kernel(D, dtype):
 
 @pytest.mark.parametrize("D", [64, 128, 256])
 def test_both_block_orders_of_the_tensor_core_kernel(D):
-    """Heads fastest (default) and all query blocks of the heads of one KV head first (default only
-    for grouped KV heads with very many query blocks): same results bit for bit, GQA with two
-    batches, zig-zag query segments, with and without cluster pairs."""
+    """(batch, head) fastest (default) and waves of 1, 2 or all 4 KV heads (default only when the
+    K/V of all heads do not fit in L2 together): same results bit for bit, GQA with two batches,
+    zig-zag query segments, with and without cluster pairs."""
     from ring_attention_b200._lib import lib
     q, k, v = normal_inputs(900 + D, 2, 6, 2, 2 * 320, 4 * 320, D, scale=0.8)
     q, k, v = (round_to(x, torch.float16) for x in (q, k, v))
@@ -311,7 +311,7 @@ def test_both_block_orders_of_the_tensor_core_kernel(D):
     want, _ = masked_truth(q, k, v, positions(qmap, 1), positions(kmap, 1), True, 0, 2)
     got = {}
     try:
-        for order in (0, 1):
+        for order in (0, 1, 2, 4):
             lib().ra_debug_set_block_order(order)
             for pair in ((False, True) if D >= 128 else (False,)):
                 got[order, pair] = run_ex(q, k, v, qmap, kmap, 1, True, torch.float16, 2, cta_pair=pair)
