@@ -89,14 +89,15 @@ template <int D, bool kPInTmem, bool kPair = false>
 struct TcCfg {
   // head_dim 256: O alone takes 256 tensor-memory columns, so a block owns ONE 128-row query
   // tile (one MMA warp, one softmax group), and a 128-key K or V tile (64 KiB) travels through
-  // the ring as four 16 KiB items of 64 head_dim columns each, consumed one by one.
+  // the ring as four 16 KiB items of 64 head_dim columns each, consumed one by one (in a CTA
+  // pair: two items per tile, 128 head_dim columns of this block's half of the tile each).
   static constexpr int kTiles = D == 256 ? 1 : 2;            // query tiles per block
   static constexpr int kThreads = 128 + 128 * kTiles;
   static constexpr int kTileBytes = kBM * D * 2;             // one 128-row tile of Q, K or V
   static constexpr int kBoxes = D / 64;                      // 64-element (128-byte) boxes per tile
   static constexpr int kItemsPerTile = D == 256 ? (kPair ? 2 : 4) : 1;  // ring items per K / V tile
   static constexpr int kBoxesPerItem = kBoxes / kItemsPerTile;
-  // CTA pair (head_dim 128, P in tensor memory): the two blocks of a cluster work on one key
+  // CTA pair (head_dim 128 / 256, P in tensor memory): the two blocks of a cluster work on one key
   // tile with M = 256 instructions. Each block loads and holds HALF of every K tile (64 of its
   // 128 keys: the N columns of S it contributes) and half of every V tile (64 of the 128
   // head_dim columns: the N columns of O), so a block's shared-memory reads per score tile drop
